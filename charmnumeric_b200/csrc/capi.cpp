@@ -1,0 +1,229 @@
+// extern "C" surface declared in include/cnb200.h.
+#include <cstring>
+#include <new>
+
+#include "../../include/cnb200.h"
+#include "context.hpp"
+
+struct cn_context {
+    cn::Context impl;
+    cn_context(int d, int r, int n) : impl(d, r, n) {}
+};
+
+namespace {
+thread_local std::string g_create_error;
+
+void copy_err(const std::string& s, char* err, int cap) {
+    if (!err || cap <= 0) return;
+    size_t n = std::min<size_t>(s.size(), (size_t)cap - 1);
+    memcpy(err, s.data(), n);
+    err[n] = 0;
+}
+}  // namespace
+
+extern "C" {
+
+int cn_version(void) { return 100; }
+
+const char* cn_status_string(int status) { return cn::status_string(status); }
+
+int cn_context_create(int device, int rank, int nranks, cn_context** out) {
+    if (!out) return cn::CN_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    cn_context* c = new (std::nothrow) cn_context(device, rank, nranks);
+    if (!c) return cn::CN_ERR_OUT_OF_MEMORY;
+    int rc = c->impl.init();
+    if (rc) {
+        g_create_error = c->impl.last_error();
+        delete c;
+        return rc;
+    }
+    *out = c;
+    return cn::CN_OK;
+}
+
+int cn_context_destroy(cn_context* ctx) {
+    delete ctx;
+    return cn::CN_OK;
+}
+
+const char* cn_last_error(cn_context* ctx) {
+    if (!ctx) return g_create_error.c_str();
+    return ctx->impl.last_error().c_str();
+}
+
+int cn_comm_unique_id(char id[128]) {
+    std::string err;
+    int rc = cn::comm_unique_id(id, &err);
+    if (rc) g_create_error = err;
+    return rc;
+}
+
+int cn_comm_init(cn_context* ctx, const char id[128]) {
+    if (!ctx || !id) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.comm_init_id(id);
+}
+
+int cn_mark_rank_failed(cn_context* ctx, int rank) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.mark_rank_failed(rank);
+}
+
+int cn_receive_dag(cn_context* ctx, int epoch, int64_t size, const char* msg) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.receive_dag(epoch, size, msg);
+}
+
+int cn_get(cn_context* ctx, int ndims, int epoch, int name, int64_t count, int dtype, void* out) {
+    (void)ndims;
+    (void)epoch;
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.get(name, count, dtype, out);
+}
+
+int cn_get_local(cn_context* ctx, int name, int64_t* row_begin, int64_t* row_end, int64_t capacity,
+                 void* out) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.get_local(name, row_begin, row_end, capacity, out);
+}
+
+int cn_put(cn_context* ctx, int name, int ndims, const int64_t* shape, int dtype, const void* host) {
+    if (!ctx || !shape) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.put(name, ndims, shape, dtype, host);
+}
+
+int cn_delete_array(cn_context* ctx, int name) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.delete_array(name);
+}
+
+int cn_array_info(cn_context* ctx, int name, int* ndims, int64_t shape[3], int* dtype,
+                  int64_t* row_begin, int64_t* row_end) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.array_info(name, ndims, shape, dtype, row_begin, row_end);
+}
+
+int cn_synchronize(cn_context* ctx) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.synchronize();
+}
+
+int cn_compile_group(cn_context* ctx, const char* node_blob, int64_t size, uint64_t* handle) {
+    if (!ctx || !handle) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.compile_group(node_blob, size, handle);
+}
+
+int cn_group_source(cn_context* ctx, uint64_t handle, const char** source) {
+    if (!ctx || !source) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.group_source(handle, source);
+}
+
+int cn_launch_group(cn_context* ctx, uint64_t handle, int n_in, void* const* in_ptrs,
+                    const int64_t* in_off, const int64_t* in_str, int n_bc, void* const* bc_ptrs,
+                    int n_out, void* const* out_ptrs, const int64_t* out_off,
+                    const int64_t* out_str, const int64_t* ext) {
+    if (!ctx || !ext) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.launch_group(handle, n_in, in_ptrs, in_off, in_str, n_bc, bc_ptrs, n_out,
+                                  out_ptrs, out_off, out_str, ext);
+}
+
+int cn_dag_check(const char* msg, int64_t size, int* n_nodes, int* n_roots, char* err, int errcap) {
+    cn::Dag dag;
+    std::string e;
+    int rc = cn::parse_dag(msg, size, &dag, &e);
+    copy_err(e, err, errcap);
+    if (rc) return rc;
+    if (n_nodes) *n_nodes = (int)dag.nodes.size();
+    if (n_roots) {
+        int n = 0;
+        for (auto& nd : dag.nodes) n += (int)nd.roots.size();
+        *n_roots = n;
+    }
+    return cn::CN_OK;
+}
+
+int cn_group_compile_check(const char* node_blob, int64_t size, char* source, int64_t cap,
+                           int64_t* cubin_bytes, char* err, int errcap) {
+    cn::DagNode node;
+    std::string e;
+    int rc = cn::parse_node(node_blob, size, &node, &e);
+    if (rc) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    // trailing REDUCE / SUM roots of a fusible group are its fused reductions
+    cn::GroupIR g;
+    rc = cn::lower_group(node, {}, &g, &e);
+    if (rc) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    std::string src;
+    rc = cn::generate_source(g, &src, &e);
+    if (rc) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    if (source && cap > 0) {
+        size_t n = std::min<size_t>(src.size(), (size_t)cap - 1);
+        memcpy(source, src.data(), n);
+        source[n] = 0;
+    }
+    std::vector<char> cubin;
+    std::string log;
+    cn::TileConfig tile;
+    rc = cn::nvrtc_compile(src, tile, &cubin, &log);
+    if (rc) {
+        copy_err(log, err, errcap);
+        return rc;
+    }
+    if (cubin_bytes) *cubin_bytes = (int64_t)cubin.size();
+    return cn::CN_OK;
+}
+
+int cn_timer_start(cn_context* ctx) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.timer_start();
+}
+
+int cn_timer_stop(cn_context* ctx, float* milliseconds) {
+    if (!ctx || !milliseconds) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.timer_stop(milliseconds);
+}
+
+int cn_get_stats(cn_context* ctx, cn_stats* out) {
+    if (!ctx || !out) return cn::CN_ERR_INVALID_ARGUMENT;
+    const cn::Stats& s = ctx->impl.stats();
+    out->kernel_launches = s.kernel_launches;
+    out->group_launches = s.group_launches;
+    out->compiles = s.compiles;
+    out->halo_exchanges = s.halo_exchanges;
+    out->allreduces = s.allreduces;
+    out->fused_reductions = s.fused_reductions;
+    out->nodes = s.nodes;
+    out->bytes_h2d = s.bytes_h2d;
+    out->bytes_d2h = s.bytes_d2h;
+    return cn::CN_OK;
+}
+
+int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
+    if (!ctx || !key) return cn::CN_ERR_INVALID_ARGUMENT;
+    std::string k(key);
+    if (k == "halo") {
+        if (value < 0 || value > 8) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_halo((int)value);
+    } else if (k == "fuse_reductions") {
+        ctx->impl.set_fuse_reductions(value != 0);
+    } else if (k == "tile_tx") {
+        if (value < 8 || value > 256 || 256 % value) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_tile((int)value, -1);
+    } else if (k == "tile_rows") {
+        if (value < 1 || value > 16) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_tile(-1, (int)value);
+    } else {
+        return cn::CN_ERR_INVALID_ARGUMENT;
+    }
+    return cn::CN_OK;
+}
+
+}  // extern "C"

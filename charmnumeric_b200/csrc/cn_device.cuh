@@ -1,0 +1,175 @@
+// Device-side support header shared by the ahead-of-time kernels (nvcc) and by every
+// kernel the DAG-group compiler generates at run time (NVRTC receives this text verbatim).
+// It must therefore compile without any standard or CUDA toolkit header.
+//
+// Contents: the launch-argument block of a fused group kernel, the exp/tanh routines,
+// and the block / grid reduction helpers with the deterministic last-block finish.
+#ifndef CN_DEVICE_CUH
+#define CN_DEVICE_CUH
+
+#define CN_MAX_IN 16
+#define CN_MAX_OUT 8
+#define CN_MAX_BC 8
+#define CN_MAX_SC 16
+#define CN_MAX_RED 4
+#define CN_MAX_SOUT 4
+#define CN_BLOCK 256
+
+// Launch arguments of one fused group kernel.  The same layout is used by the host
+// (it fills the block) and by the generated source (it reads it), so only plain types.
+struct CnGroupArgs {
+    const void* in[CN_MAX_IN];   // array leaves: address of local element (0,0,0)
+    void* out[CN_MAX_OUT];       // outputs: address of local element (0,0,0) of the buffer written
+    const void* old[CN_MAX_OUT]; // previous contents of each output array
+    const void* bc[CN_MAX_BC];   // size-1 arrays read as scalars
+    void* sout[CN_MAX_SOUT];     // size-1 arrays written by scalar roots
+    double sc[CN_MAX_SC];        // literal scalars, cast to the element type in the kernel
+    long long lo[3], hi[3];      // iteration box [lo,hi) in the frame's local coordinates
+    long long rlo[3], rhi[3];    // region box: where SET_REGION outputs are computed
+    long long stride[3];         // element strides of the common array shape (shifted class)
+    long long in_off[CN_MAX_IN];     // strided class: element offset of each leaf view
+    long long in_str[CN_MAX_IN][3];  // strided class: element stride per iteration dim
+    long long out_off[CN_MAX_OUT];
+    long long out_str[CN_MAX_OUT][3];
+    long long ext[3];            // strided class: iteration extents
+    long long ntiles;            // number of tiles the persistent blocks walk over
+    long long ntx, nty;          // tiles along the last and the second-to-last dimension
+    double* partials;            // [CN_MAX_RED][gridDim.x] per-block partial sums
+    unsigned int* counter;       // ticket for the last-block finish (left at 0 on exit)
+    void* red[CN_MAX_RED];       // reduction results (size-1 arrays)
+};
+
+#ifdef __CUDACC__
+
+#include "cn_exp_table.inc"
+
+__device__ const double cn_exp_hi[64] = {CN_EXP_TABLE_HI};
+__device__ const double cn_exp_lo[64] = {CN_EXP_TABLE_LO};
+
+// 2^m * v for v in [1, 4): one exponent-field add when the result stays normal, two
+// exact power-of-two multiplies otherwise (gradual underflow / overflow to inf).
+__device__ __forceinline__ double cn_scale2(double v, int m) {
+    if (m >= -1000 && m <= 1000) {
+        long long bits = __double_as_longlong(v) + ((long long)m << 52);
+        return __longlong_as_double(bits);
+    }
+    int m1 = m / 2, m2 = m - m1;
+    double p1 = __longlong_as_double((long long)(m1 + 1023) << 52);
+    double p2 = __longlong_as_double((long long)(m2 + 1023) << 52);
+    return (v * p1) * p2;
+}
+
+// exp(x) = 2^m * 2^(j/64) * e^r with |r| <= ln2/128; degree-5 polynomial for e^r - 1.
+// Every step is an explicitly rounded IEEE operation (fma / mul / add), so the host
+// restatement that performs the same steps with C fma() gives identical bits.
+__device__ __forceinline__ double cn_exp(double x) {
+    if (!(x == x)) return x;
+    if (x > 709.782712893384) return __longlong_as_double(0x7ff0000000000000LL);
+    if (x < -745.1332191019412) return 0.0;
+    const double shift = 6755399441055744.0;  // 1.5 * 2^52
+    double t = __fma_rn(x, CN_INV_LN2_64, shift);
+    int ki = (int)(unsigned int)(__double_as_longlong(t) & 0xffffffffLL);
+    double kd = t - shift;
+    double r = __fma_rn(-kd, CN_LN2_64_HI, x);
+    r = __fma_rn(-kd, CN_LN2_64_LO, r);
+    int j = ki & 63;
+    int m = ki >> 6;
+    double p = __fma_rn(r, 0x1.1111111111111p-7, 0x1.5555555555555p-5);  // 1/120, 1/24
+    p = __fma_rn(p, r, 0x1.5555555555555p-3);                            // 1/6
+    p = __fma_rn(p, r, 0.5);
+    double q = __fma_rn(p, r * r, r);                                     // e^r - 1
+    double hi = cn_exp_hi[j], lo = cn_exp_lo[j];
+    double v = hi + __fma_rn(hi, q, lo);
+    return cn_scale2(v, m);
+}
+
+// expm1(y) for 0 <= y <= 1.1 with the same reduction; (hi*2^m - 1) is exact there.
+__device__ __forceinline__ double cn_expm1_small(double y) {
+    const double shift = 6755399441055744.0;
+    double t = __fma_rn(y, CN_INV_LN2_64, shift);
+    int ki = (int)(unsigned int)(__double_as_longlong(t) & 0xffffffffLL);
+    double kd = t - shift;
+    double r = __fma_rn(-kd, CN_LN2_64_HI, y);
+    r = __fma_rn(-kd, CN_LN2_64_LO, r);
+    int j = ki & 63;
+    int m = ki >> 6;
+    // two more terms than exp: the result is small, so the absolute error must be too
+    double p = __fma_rn(r, 0x1.a01a01a01a01ap-13, 0x1.6c16c16c16c17p-10);  // 1/5040, 1/720
+    p = __fma_rn(p, r, 0x1.1111111111111p-7);
+    p = __fma_rn(p, r, 0x1.5555555555555p-5);
+    p = __fma_rn(p, r, 0x1.5555555555555p-3);
+    p = __fma_rn(p, r, 0.5);
+    double q = __fma_rn(p, r * r, r);
+    double sc = (m == 0) ? 1.0 : ((m == 1) ? 2.0 : 4.0);
+    double hi = cn_exp_hi[j] * sc, lo = cn_exp_lo[j] * sc;
+    return (hi - 1.0) + __fma_rn(hi, q, lo);
+}
+
+__device__ __forceinline__ double cn_tanh(double x) {
+    if (!(x == x)) return x;
+    double ax = x < 0 ? -x : x;
+    double r;
+    if (ax >= 22.0) {
+        r = 1.0;
+    } else if (ax >= 0.5) {
+        double e = cn_exp(2.0 * ax);
+        r = 1.0 - 2.0 / (e + 1.0);
+    } else if (ax >= 0x1p-28) {
+        double em1 = cn_expm1_small(2.0 * ax);
+        r = em1 / (em1 + 2.0);
+    } else {
+        r = ax;
+    }
+    return x < 0 ? -r : r;
+}
+
+// ---- reductions -------------------------------------------------------------------
+// Fixed-shape tree: xor-shuffle inside each warp, then warp 0 folds the per-warp sums
+// in lane order.  The same block size always gives the same association order.
+template <typename A>
+__device__ __forceinline__ A cn_warp_sum(A v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <typename A>
+__device__ __forceinline__ A cn_block_sum(A v, A* smem /* >= 32 entries */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = cn_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    A t = (threadIdx.x < nwarp) ? smem[threadIdx.x] : (A)0;
+    if (warp == 0) t = cn_warp_sum(t);
+    return t;  // valid in thread 0
+}
+
+// Deterministic two-pass finish inside one launch: every block stores its partials, then
+// draws a ticket; the block that draws the last ticket re-reads all partials in index
+// order and writes the totals.  No block waits on another, and the ticket counter is
+// put back to 0 for the next launch.  Returns true in every thread of the last block.
+__device__ __forceinline__ bool cn_grid_ticket(unsigned int* counter, int* flag_shared) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int ticket = atomicAdd(counter, 1u);
+        *flag_shared = (ticket == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    bool last = (*flag_shared != 0);
+    if (last) __threadfence();
+    return last;
+}
+
+template <typename A>
+__device__ __forceinline__ A cn_sum_partials(const A* partials, A* smem) {
+    A v = (A)0;
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += blockDim.x)
+        v += ((const volatile A*)partials)[i];
+    return cn_block_sum(v, smem);  // valid in thread 0
+}
+
+#endif  // __CUDACC__
+#endif  // CN_DEVICE_CUH

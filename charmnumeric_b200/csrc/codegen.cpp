@@ -1,0 +1,459 @@
+// GroupIR -> CUDA source for one fused group kernel (entry point `cn_group`).
+//
+// The reference builds one linalg.generic per root and relies on MLIR loop fusion
+// (src/jit.cpp:28-185), then launches one 256-thread-per-block kernel per aligned fragment
+// (src/dispatch.hpp:187-194).  Here each group becomes ONE persistent kernel over the whole
+// local slab: blocks walk a list of tiles, every thread owns `vec` adjacent elements of
+// `CN_R` consecutive rows, loads are 128-bit where the column offset is even, every root is
+// one separately rounded statement (the program is compiled with --fmad=false so that
+// a*b+c is never contracted), and fused reductions end in the deterministic last-block
+// finish of cn_device.cuh.
+#include <map>
+#include <set>
+#include <sstream>
+
+#include "cn_device.cuh"
+#include "group_ir.hpp"
+
+namespace cn {
+
+namespace {
+
+const char* type_name(int dt) {
+    switch (dt) {
+        case DT_F32: return "float";
+        case DT_F64: return "double";
+        case DT_I32: return "int";
+        default: return "long long";
+    }
+}
+
+struct Gen {
+    const GroupIR& g;
+    std::ostringstream o;
+    bool is_float() const { return g.dtype == DT_F32 || g.dtype == DT_F64; }
+    int nd() const { return g.flat ? 1 : g.ndims; }
+
+    std::string val(const ValRef& v, int e) const {
+        std::ostringstream s;
+        switch (v.kind) {
+            case ValRef::LEAF: s << "l" << v.idx << "_" << e; break;
+            case ValRef::CONST: s << "c" << v.idx; break;
+            case ValRef::BCAST: s << "b" << v.idx; break;
+            case ValRef::ROOT:
+                if (g.roots[v.idx].domain == DOM_SCALAR) s << "r" << v.idx;
+                else s << "r" << v.idx << "_" << e;
+                break;
+            case ValRef::OUTVAL: s << "w" << v.idx << "_" << e; break;
+            default: s << "(T)0";
+        }
+        return s.str();
+    }
+
+    std::string expr(int opcode, const std::string& a, const std::string& b) const {
+        switch (opcode) {
+            case OP_ADD: return a + " + " + b;
+            case OP_SUB: return a + " - " + b;
+            case OP_MUL: return a + " * " + b;
+            case OP_DIV: return a + " / " + b;
+            case OP_COPY: return a;
+            case OP_EXP:
+                return g.dtype == DT_F64 ? "cn_exp(" + a + ")" : "(T)cn_exp((double)" + a + ")";
+            case OP_TANH:
+                return g.dtype == DT_F64 ? "cn_tanh(" + a + ")" : "(T)cn_tanh((double)" + a + ")";
+            case OP_SQRT: return g.dtype == DT_F64 ? "sqrt(" + a + ")" : "sqrtf(" + a + ")";
+            case OP_ABS:
+                if (g.dtype == DT_F64) return "fabs(" + a + ")";
+                if (g.dtype == DT_F32) return "fabsf(" + a + ")";
+                return "(" + a + " < 0 ? -" + a + " : " + a + ")";
+        }
+        return "(T)0";
+    }
+
+    // slot of each distinct input array, in order of first use (SHIFTED class)
+    std::vector<int> in_names;
+    int in_slot(int name) {
+        for (size_t i = 0; i < in_names.size(); ++i)
+            if (in_names[i] == name) return (int)i;
+        in_names.push_back(name);
+        return (int)in_names.size() - 1;
+    }
+    // an input buffer may be the very buffer an output is written to (in-place update)
+    bool aliases_written_buffer(int name) const {
+        for (auto& out : g.outs)
+            if (out.name == name && out.is_set && !(g.copy_through && out.hazard)) return true;
+        return false;
+    }
+    bool any_inplace() const {
+        for (auto& out : g.outs)
+            if (out.is_set && !(g.copy_through && out.hazard)) return true;
+        return false;
+    }
+
+    void prologue() {
+        o << "#include \"cn_device.cuh\"\n";
+        o << "typedef " << type_name(g.dtype) << " T;\n";
+        o << "typedef " << (is_float() ? "double" : "long long") << " ACC;\n";
+        if (g.vec == 2) o << "typedef double2 T2;\n";
+        o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK) cn_group("
+             "const __grid_constant__ CnGroupArgs a) {\n";
+        for (size_t i = 0; i < g.scalars.size(); ++i)
+            o << "  const T c" << i << " = (T)a.sc[" << i << "];\n";
+        for (size_t i = 0; i < g.bcast_names.size(); ++i)
+            o << "  const T b" << i << " = *(const T*)a.bc[" << i << "];\n";
+        for (size_t i = 0; i < g.roots.size(); ++i) {
+            const RootIR& r = g.roots[i];
+            if (r.domain != DOM_SCALAR) continue;
+            o << "  const T r" << i << " = " << expr(r.opcode, val(r.a, 0), val(r.b, 0)) << ";\n";
+        }
+    }
+
+    void scalar_outs() {
+        if (g.souts.empty()) return;
+        o << "  if (blockIdx.x == 0 && threadIdx.x == 0) {\n";
+        for (size_t i = 0; i < g.souts.size(); ++i)
+            o << "    *(T*)a.sout[" << i << "] = " << val(g.souts[i].value, 0) << ";\n";
+        o << "  }\n";
+    }
+
+    void red_decl() {
+        for (size_t i = 0; i < g.reds.size(); ++i) o << "  ACC acc" << i << " = (ACC)0;\n";
+    }
+
+    void red_epilogue() {
+        if (g.reds.empty()) return;
+        o << "  __shared__ ACC cn_sm[32];\n  __shared__ int cn_flag;\n";
+        for (size_t i = 0; i < g.reds.size(); ++i)
+            o << "  ACC bt" << i << " = cn_block_sum(acc" << i << ", cn_sm);\n";
+        o << "  if (threadIdx.x == 0) {\n";
+        for (size_t i = 0; i < g.reds.size(); ++i)
+            o << "    ((ACC*)a.partials)[" << i << " * gridDim.x + blockIdx.x] = bt" << i << ";\n";
+        o << "  }\n";
+        o << "  if (cn_grid_ticket(a.counter, &cn_flag)) {\n";
+        for (size_t i = 0; i < g.reds.size(); ++i) {
+            o << "    ACC t" << i << " = cn_sum_partials(((const ACC*)a.partials) + " << i
+              << " * gridDim.x, cn_sm);\n";
+            o << "    if (threadIdx.x == 0) *(T*)a.red[" << i << "] = (T)t" << i << ";\n";
+        }
+        o << "    if (threadIdx.x == 0) *a.counter = 0u;\n";
+        o << "  }\n";
+    }
+
+    std::string guard(int domain, int e) const {
+        std::ostringstream s;
+        s << ((domain == DOM_REGION && g.two_domains) ? "act" : "bx") << e;
+        return s.str();
+    }
+    std::string guard_any(int domain) const {
+        std::string base = (domain == DOM_REGION && g.two_domains) ? "act" : "bx";
+        if (g.vec == 1) return "(" + base + "0)";
+        return "(" + base + "0 | " + base + "1)";
+    }
+
+    // ---- SHIFTED class ----------------------------------------------------------------
+    void shifted_body(const std::string& ind) {
+        const int N = nd();
+        const int V = g.vec;
+        // row offset expression of a leaf: deltas of all but the last dimension
+        auto rowoff = [&](const LeafIR& l) {
+            std::ostringstream s;
+            if (g.flat) return std::string("");
+            if (N == 2 && l.delta[0]) s << " + (" << l.delta[0] << "LL) * s0";
+            if (N == 3) {
+                if (l.delta[0]) s << " + (" << l.delta[0] << "LL) * s0";
+                if (l.delta[1]) s << " + (" << l.delta[1] << "LL) * s1";
+            }
+            return s.str();
+        };
+        // group leaves into rows: (array, domain, outer deltas)
+        struct Row {
+            int name, domain;
+            int64_t d0, d1;
+            std::string off;
+            std::set<int64_t> cols;
+        };
+        std::vector<Row> rows;
+        std::vector<int> leaf_row(g.leaves.size());
+        for (size_t k = 0; k < g.leaves.size(); ++k) {
+            const LeafIR& l = g.leaves[k];
+            int64_t d0 = 0, d1 = 0, dl = 0;
+            if (!g.flat) {
+                if (N == 1) dl = l.delta[0];
+                if (N == 2) d0 = l.delta[0], dl = l.delta[1];
+                if (N == 3) d0 = l.delta[0], d1 = l.delta[1], dl = l.delta[2];
+            }
+            int found = -1;
+            for (size_t r = 0; r < rows.size(); ++r)
+                if (rows[r].name == l.name && rows[r].domain == l.domain && rows[r].d0 == d0 &&
+                    rows[r].d1 == d1)
+                    found = (int)r;
+            if (found < 0) {
+                Row r{l.name, l.domain, d0, d1, rowoff(l), {}};
+                rows.push_back(r);
+                found = (int)rows.size() - 1;
+            }
+            leaf_row[k] = found;
+            for (int e = 0; e < V; ++e) rows[found].cols.insert(dl + e);
+        }
+        auto colname = [](int row, int64_t c) {
+            std::ostringstream s;
+            s << "m" << row << (c < 0 ? "n" : "p") << (c < 0 ? -c : c);
+            return s.str();
+        };
+        // loads
+        for (size_t r = 0; r < rows.size(); ++r) {
+            Row& row = rows[r];
+            int slot = in_slot(row.name);
+            std::ostringstream decl;
+            for (int64_t c : row.cols) decl << ind << "T " << colname((int)r, c) << " = (T)0;\n";
+            o << decl.str();
+            o << ind << "if " << guard_any(row.domain) << " {\n";
+            std::set<int64_t> done;
+            for (int64_t c : row.cols) {
+                if (done.count(c)) continue;
+                bool even = ((c % 2) + 2) % 2 == 0;
+                if (V == 2 && even && row.cols.count(c + 1)) {
+                    o << ind << "  { const T2 q = *(const T2*)(in" << slot << " + p" << row.off
+                      << " + (" << c << "LL)); " << colname((int)r, c) << " = q.x; "
+                      << colname((int)r, c + 1) << " = q.y; }\n";
+                    done.insert(c);
+                    done.insert(c + 1);
+                } else {
+                    o << ind << "  " << colname((int)r, c) << " = in" << slot << "[p" << row.off
+                      << " + (" << c << "LL)];\n";
+                    done.insert(c);
+                }
+            }
+            o << ind << "}\n";
+        }
+        for (size_t k = 0; k < g.leaves.size(); ++k) {
+            const LeafIR& l = g.leaves[k];
+            int64_t dl = g.flat ? 0 : l.delta[N - 1];
+            for (int e = 0; e < V; ++e)
+                o << ind << "const T l" << k << "_" << e << " = " << colname(leaf_row[k], dl + e)
+                  << ";\n";
+        }
+        // old contents of outputs
+        for (size_t m = 0; m < g.outs.size(); ++m) {
+            if (!g.outs[m].needs_old) continue;
+            for (int e = 0; e < V; ++e) o << ind << "T old" << m << "_" << e << " = (T)0;\n";
+            o << ind << "if " << guard_any(DOM_BOX) << " {\n";
+            if (V == 2) {
+                o << ind << "  const T2 q = *(const T2*)(old" << m << " + p);\n";
+                o << ind << "  old" << m << "_0 = q.x; old" << m << "_1 = q.y;\n";
+            } else {
+                o << ind << "  old" << m << "_0 = old" << m << "[p];\n";
+            }
+            o << ind << "}\n";
+        }
+        auto emit_merged = [&](size_t m) {
+            const OutIR& out = g.outs[m];
+            for (int e = 0; e < V; ++e) {
+                o << ind << "const T w" << m << "_" << e << " = ";
+                if (out.needs_old)
+                    o << guard(out.domain, e) << " ? " << val(out.value, e) << " : old" << m << "_"
+                      << e << ";\n";
+                else
+                    o << val(out.value, e) << ";\n";
+            }
+        };
+        for (size_t m = 0; m < g.outs.size(); ++m)
+            if (g.outs[m].value.kind != ValRef::ROOT ||
+                g.roots[g.outs[m].value.idx].domain == DOM_SCALAR)
+                emit_merged(m);
+        for (size_t i = 0; i < g.roots.size(); ++i) {
+            const RootIR& r = g.roots[i];
+            if (r.domain == DOM_SCALAR) continue;
+            for (int e = 0; e < V; ++e)
+                o << ind << "const T r" << i << "_" << e << " = "
+                  << expr(r.opcode, val(r.a, e), val(r.b, e)) << ";\n";
+            for (size_t m = 0; m < g.outs.size(); ++m)
+                if (g.outs[m].value.kind == ValRef::ROOT && g.outs[m].value.idx == (int)i)
+                    emit_merged(m);
+        }
+        // stores
+        for (size_t m = 0; m < g.outs.size(); ++m) {
+            const OutIR& out = g.outs[m];
+            int dom = (g.copy_through && out.hazard) ? DOM_BOX : out.domain;
+            if (V == 2) {
+                o << ind << "if (" << guard(dom, 0) << " & " << guard(dom, 1) << ") {\n";
+                o << ind << "  T2 q; q.x = w" << m << "_0; q.y = w" << m << "_1;\n";
+                o << ind << "  *(T2*)(out" << m << " + p) = q;\n";
+                o << ind << "} else if (" << guard(dom, 0) << ") {\n";
+                o << ind << "  out" << m << "[p] = w" << m << "_0;\n";
+                o << ind << "} else if (" << guard(dom, 1) << ") {\n";
+                o << ind << "  out" << m << "[p + 1] = w" << m << "_1;\n";
+                o << ind << "}\n";
+            } else {
+                o << ind << "if (" << guard(dom, 0) << ") out" << m << "[p] = w" << m << "_0;\n";
+            }
+        }
+        // reductions
+        for (size_t q = 0; q < g.reds.size(); ++q) {
+            const RedIR& rd = g.reds[q];
+            for (int e = 0; e < V; ++e) {
+                std::string prod = rd.b.kind == ValRef::NONE
+                                       ? "(ACC)" + val(rd.a, e)
+                                       : "(ACC)(" + val(rd.a, e) + " * " + val(rd.b, e) + ")";
+                o << ind << "if (" << guard(rd.domain, e) << ") acc" << q << " += " << prod
+                  << ";\n";
+            }
+        }
+    }
+
+    void shifted() {
+        const int N = nd();
+        const int V = g.vec;
+        prologue();
+        scalar_outs();
+        // resolve input slots first so the pointer declarations are complete
+        for (auto& l : g.leaves) in_slot(l.name);
+        const bool inplace = any_inplace();
+        for (size_t i = 0; i < in_names.size(); ++i) {
+            bool alias = inplace && aliases_written_buffer(in_names[i]);
+            o << "  const T* " << (alias ? "" : "__restrict__ ") << "in" << i << " = (const T*)a.in["
+              << i << "];\n";
+        }
+        for (size_t m = 0; m < g.outs.size(); ++m) {
+            bool shadow = g.copy_through && g.outs[m].hazard;
+            o << "  T* " << (shadow ? "__restrict__ " : "") << "out" << m << " = (T*)a.out[" << m
+              << "];\n";
+            if (g.outs[m].needs_old)
+                o << "  const T* old" << m << " = (const T*)a.old[" << m << "];\n";
+        }
+        red_decl();
+        const int L = N - 1;
+        if (N >= 2) o << "  const long long s0 = a.stride[0];\n";
+        if (N == 3) o << "  const long long s1 = a.stride[1];\n";
+        o << "  const long long xlo = a.lo[" << L << "], xhi = a.hi[" << L << "];\n";
+        if (g.two_domains)
+            o << "  const long long rxlo = a.rlo[" << L << "], rxhi = a.rhi[" << L << "];\n";
+        o << "  const long long xbase = " << (V == 2 ? "xlo & ~1LL" : "xlo") << ";\n";
+        o << "  const unsigned int ntiles = (unsigned int)a.ntiles;\n";
+        if (N == 1) {
+            o << "  for (unsigned int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+            o << "#pragma unroll\n";
+            o << "    for (int r = 0; r < CN_R; ++r) {\n";
+            o << "      const long long x = xbase + ((long long)tile * CN_R + r) * (CN_BLOCK * " << V
+              << ") + threadIdx.x * " << V << ";\n";
+            o << "      const long long p = x;\n";
+        } else {
+            o << "  const unsigned int ntx = (unsigned int)a.ntx;\n";
+            if (N == 3) o << "  const unsigned int nty = (unsigned int)a.nty;\n";
+            o << "  const int lx = threadIdx.x % CN_TX, ly = threadIdx.x / CN_TX;\n";
+            o << "  for (unsigned int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+            o << "    const unsigned int tx = tile % ntx; const unsigned int t2 = tile / ntx;\n";
+            if (N == 3) {
+                o << "    const unsigned int ty = t2 % nty;\n";
+                o << "    const long long z = a.lo[0] + (long long)(t2 / nty);\n";
+            } else {
+                o << "    const unsigned int ty = t2;\n";
+            }
+            o << "    const long long x = xbase + ((long long)tx * CN_TX + lx) * " << V << ";\n";
+            o << "    const long long ybase = a.lo[" << (N - 2) << "] + ((long long)ty * (CN_BLOCK / CN_TX) + ly) * CN_R;\n";
+            o << "#pragma unroll\n";
+            o << "    for (int r = 0; r < CN_R; ++r) {\n";
+            o << "      const long long y = ybase + r;\n";
+            o << "      if (y >= a.hi[" << (N - 2) << "]) break;\n";
+            if (N == 2) o << "      const long long p = y * s0 + x;\n";
+            else o << "      const long long p = z * s0 + y * s1 + x;\n";
+        }
+        for (int e = 0; e < V; ++e)
+            o << "      const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
+              << " < xhi);\n";
+        if (g.two_domains) {
+            std::ostringstream rowin;
+            rowin << "true";
+            if (N == 2) rowin << " & (y >= a.rlo[0]) & (y < a.rhi[0])";
+            if (N == 3)
+                rowin << " & (z >= a.rlo[0]) & (z < a.rhi[0]) & (y >= a.rlo[1]) & (y < a.rhi[1])";
+            o << "      const bool rowin = " << rowin.str() << ";\n";
+            for (int e = 0; e < V; ++e)
+                o << "      const bool act" << e << " = rowin & (x + " << e << " >= rxlo) & (x + "
+                  << e << " < rxhi);\n";
+        }
+        o << "      if " << guard_any(DOM_BOX) << " {\n";
+        shifted_body("        ");
+        o << "      }\n";
+        o << "    }\n";
+        o << "  }\n";
+        red_epilogue();
+        o << "}\n";
+    }
+
+    // ---- STRIDED class ----------------------------------------------------------------
+    void strided() {
+        const int N = g.ndims;
+        prologue();
+        scalar_outs();
+        for (size_t k = 0; k < g.leaves.size(); ++k)
+            o << "  const T* in" << k << " = (const T*)a.in[" << k << "];\n";
+        for (size_t m = 0; m < g.outs.size(); ++m)
+            o << "  T* out" << m << " = (T*)a.out[" << m << "];\n";
+        red_decl();
+        o << "  const long long e0 = a.ext[0]";
+        if (N >= 2) o << ", e1 = a.ext[1]";
+        if (N == 3) o << ", e2 = a.ext[2]";
+        o << ";\n";
+        o << "  const long long total = e0" << (N >= 2 ? " * e1" : "") << (N == 3 ? " * e2" : "")
+          << ";\n";
+        o << "  for (long long i = (long long)blockIdx.x * CN_BLOCK + threadIdx.x; i < total; "
+             "i += (long long)gridDim.x * CN_BLOCK) {\n";
+        if (N == 1) o << "    const long long i0 = i;\n";
+        if (N == 2) o << "    const long long i0 = i / e1, i1 = i - i0 * e1;\n";
+        if (N == 3)
+            o << "    const long long i0 = i / (e1 * e2); const long long rem = i - i0 * e1 * e2;\n"
+                 "    const long long i1 = rem / e2, i2 = rem - i1 * e2;\n";
+        auto addr = [&](const char* what, size_t k) {
+            std::ostringstream s;
+            s << "a." << what << "_off[" << k << "] + i0 * a." << what << "_str[" << k << "][0]";
+            if (N >= 2) s << " + i1 * a." << what << "_str[" << k << "][1]";
+            if (N == 3) s << " + i2 * a." << what << "_str[" << k << "][2]";
+            return s.str();
+        };
+        for (size_t k = 0; k < g.leaves.size(); ++k)
+            o << "    const T l" << k << "_0 = in" << k << "[" << addr("in", k) << "];\n";
+        for (size_t i = 0; i < g.roots.size(); ++i) {
+            const RootIR& r = g.roots[i];
+            if (r.domain == DOM_SCALAR) continue;
+            o << "    const T r" << i << "_0 = " << expr(r.opcode, val(r.a, 0), val(r.b, 0)) << ";\n";
+        }
+        for (size_t m = 0; m < g.outs.size(); ++m)
+            o << "    out" << m << "[" << addr("out", m) << "] = " << val(g.outs[m].value, 0)
+              << ";\n";
+        for (size_t q = 0; q < g.reds.size(); ++q) {
+            const RedIR& rd = g.reds[q];
+            std::string prod = rd.b.kind == ValRef::NONE
+                                   ? "(ACC)" + val(rd.a, 0)
+                                   : "(ACC)(" + val(rd.a, 0) + " * " + val(rd.b, 0) + ")";
+            o << "    acc" << q << " += " << prod << ";\n";
+        }
+        o << "  }\n";
+        red_epilogue();
+        o << "}\n";
+    }
+
+    void scalar_only() {
+        prologue();
+        scalar_outs();
+        o << "}\n";
+    }
+};
+
+}  // namespace
+
+int generate_source(const GroupIR& g, std::string* src, std::string* err) {
+    Gen gen{g, {}, {}};
+    switch (g.cls) {
+        case GroupIR::SCALAR_ONLY: gen.scalar_only(); break;
+        case GroupIR::SHIFTED: gen.shifted(); break;
+        case GroupIR::STRIDED: gen.strided(); break;
+        default:
+            if (err) *err = "unknown group class";
+            return CN_ERR_UNSUPPORTED;
+    }
+    *src = gen.o.str();
+    return CN_OK;
+}
+
+}  // namespace cn

@@ -1,0 +1,481 @@
+#include "context.hpp"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "kernels.hpp"
+
+namespace cn {
+
+namespace {
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+Context::Context(int device, int rank, int nranks)
+    : device_(device), rank_(rank), nranks_(nranks), failed_(nranks > 0 ? nranks : 1, false) {
+    if (const char* t = getenv("CN_TILE")) {
+        int tx = 0, r = 0;
+        if (sscanf(t, "%d,%d", &tx, &r) == 2 && tx >= 8 && tx <= 256 && (256 % tx) == 0 && r >= 1 &&
+            r <= 16) {
+            tile_.tx = tx;
+            tile_.r = r;
+        }
+    }
+    if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
+}
+
+Context::~Context() {
+    if (!initialised_) return;
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    comm_destroy(&comm_);
+    for (auto& kv : arrays_) {
+        free_buffer(&kv.second.buf);
+        free_buffer(&kv.second.shadow);
+    }
+    for (auto& kv : kernels_)
+        if (kv.second.module && drv_.ModuleUnload) drv_.ModuleUnload(kv.second.module);
+    if (partials_) cudaFree(partials_);
+    if (counter_) cudaFree(counter_);
+    if (scratch_) cudaFree(scratch_);
+    if (ev_start_) cudaEventDestroy(ev_start_);
+    if (ev_stop_) cudaEventDestroy(ev_stop_);
+    cudaStreamSynchronize(stream_);
+    cudaStreamDestroy(stream_);
+}
+
+int Context::fail(int code, const std::string& msg) {
+    err_ = msg;
+    return code;
+}
+
+int Context::cuda_fail(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return CN_OK;
+    err_ = std::string(what) + ": " + cudaGetErrorString(e);
+    if (e == cudaErrorMemoryAllocation) return CN_ERR_OUT_OF_MEMORY;
+    return CN_ERR_CUDA;
+}
+
+int Context::driver_fail(CUresult r, const char* what) {
+    if (r == CUDA_SUCCESS) return CN_OK;
+    const char* s = nullptr;
+    if (drv_.GetErrorString) drv_.GetErrorString(r, &s);
+    err_ = std::string(what) + ": " + (s ? s : "driver error");
+    return CN_ERR_CUDA;
+}
+
+int Context::init() {
+    if (rank_ < 0 || nranks_ < 1 || rank_ >= nranks_)
+        return fail(CN_ERR_INVALID_ARGUMENT, "rank / nranks out of range");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(CN_ERR_NO_DEVICE, "no CUDA device is visible; this backend has no CPU path");
+    }
+    if (device_ < 0 || device_ >= count) return fail(CN_ERR_INVALID_ARGUMENT, "device index out of range");
+    int rc;
+    if ((rc = cuda_fail(cudaSetDevice(device_), "cudaSetDevice"))) return rc;
+    if ((rc = cuda_fail(cudaFree(0), "context creation"))) return rc;
+    cudaDeviceProp prop;
+    if ((rc = cuda_fail(cudaGetDeviceProperties(&prop, device_), "cudaGetDeviceProperties"))) return rc;
+    if (prop.major < 10)
+        return fail(CN_ERR_NO_DEVICE, "kernels are built for sm_100a; device is older");
+    sm_count_ = prop.multiProcessorCount;
+    if ((rc = cuda_fail(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "stream"))) return rc;
+    if ((rc = cuda_fail(cudaEventCreate(&ev_start_), "event"))) return rc;
+    if ((rc = cuda_fail(cudaEventCreate(&ev_stop_), "event"))) return rc;
+    // keep freed blocks in the stream-ordered pool: array lifetimes recycle memory
+    // (the reference keeps a 4-deep free list per shape, src/backend.hpp:366-468)
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, device_) == cudaSuccess) {
+        unsigned long long thr = ~0ULL;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr);
+    }
+    max_grid_ = sm_count_ * 16;
+    if ((rc = cuda_fail(cudaMalloc(&partials_, sizeof(double) * CN_MAX_RED * max_grid_), "scratch"))) return rc;
+    if ((rc = cuda_fail(cudaMalloc(&counter_, 256), "scratch"))) return rc;
+    if ((rc = cuda_fail(cudaMemset(counter_, 0, 256), "scratch"))) return rc;
+#define CN_DRV(field, sym)                                                                    \
+    {                                                                                         \
+        void* fp = nullptr;                                                                   \
+        cudaDriverEntryPointQueryResult q;                                                    \
+        cudaError_t de = cudaGetDriverEntryPoint(sym, &fp, cudaEnableDefault, &q);            \
+        if (de != cudaSuccess || !fp || q != cudaDriverEntryPointSuccess)                     \
+            return fail(CN_ERR_CUDA, std::string("driver entry point missing: ") + sym);      \
+        drv_.field = reinterpret_cast<decltype(drv_.field)>(fp);                              \
+    }
+    CN_DRV(ModuleLoadData, "cuModuleLoadData")
+    CN_DRV(ModuleGetFunction, "cuModuleGetFunction")
+    CN_DRV(ModuleUnload, "cuModuleUnload")
+    CN_DRV(LaunchKernel, "cuLaunchKernel")
+    CN_DRV(GetErrorString, "cuGetErrorString")
+    CN_DRV(OccupancyMaxActiveBlocksPerMultiprocessor, "cuOccupancyMaxActiveBlocksPerMultiprocessor")
+#undef CN_DRV
+    initialised_ = true;
+    return CN_OK;
+}
+
+// ---- arrays -----------------------------------------------------------------------------
+
+Array* Context::find(int name) {
+    auto it = arrays_.find(name);
+    return it == arrays_.end() ? nullptr : &it->second;
+}
+
+void Context::partition(int64_t n0, int64_t* begin, int64_t* end, int r) const {
+    int64_t per = (n0 + nranks_ - 1) / nranks_;
+    *begin = std::min<int64_t>((int64_t)r * per, n0);
+    *end = std::min<int64_t>((int64_t)(r + 1) * per, n0);
+}
+
+int Context::alloc_buffer(const Array& a, Buffer* b) {
+    const size_t esz = dtype_size(a.dtype);
+    const size_t halo_bytes = (size_t)a.halo * a.unit * esz;
+    const size_t front = round_up(halo_bytes + 64, 256);
+    const size_t total = front + (size_t)a.local_elems() * esz + halo_bytes + 256;
+    void* p = nullptr;
+    cudaError_t e = cudaMallocAsync(&p, total, stream_);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMallocAsync");
+    b->alloc = p;
+    b->data = (char*)p + front;
+    b->bytes = total;
+    return CN_OK;
+}
+
+void Context::free_buffer(Buffer* b) {
+    if (b->alloc) cudaFreeAsync(b->alloc, stream_);
+    b->alloc = nullptr;
+    b->data = nullptr;
+    b->bytes = 0;
+}
+
+int Context::create_array(int name, int ndims, const int64_t* shape, int dtype, bool zero,
+                          Array** out) {
+    if (ndims < 1 || ndims > kMaxDims) return fail(CN_ERR_INVALID_ARGUMENT, "array rank must be 1..3");
+    if (!dtype_valid(dtype)) return fail(CN_ERR_BAD_DTYPE, "bad dtype code");
+    for (int d = 0; d < ndims; ++d)
+        if (shape[d] < 0) return fail(CN_ERR_INVALID_ARGUMENT, "negative extent");
+    Array* old = find(name);
+    if (old) {
+        bool same = old->ndims == ndims && old->dtype == dtype;
+        for (int d = 0; same && d < ndims; ++d) same = old->shape[d] == shape[d];
+        if (same) {
+            if (zero) {
+                int rc = cuda_fail(cudaMemsetAsync(old->buf.alloc, 0, old->buf.bytes, stream_), "memset");
+                if (rc) return rc;
+                old->halo_valid = false;
+            }
+            if (out) *out = old;
+            return CN_OK;
+        }
+        free_buffer(&old->buf);
+        free_buffer(&old->shadow);
+        arrays_.erase(name);
+    }
+    Array a;
+    a.name = name;
+    a.ndims = ndims;
+    a.dtype = dtype;
+    for (int d = 0; d < ndims; ++d) a.shape[d] = shape[d];
+    a.unit = 1;
+    for (int d = 1; d < ndims; ++d) a.unit *= shape[d];
+    a.replicated = a.global_elems() == 1;
+    if (a.replicated || nranks_ == 1) {
+        a.row_begin = 0;
+        a.row_end = shape[0];
+        a.halo = 0;
+    } else {
+        partition(shape[0], &a.row_begin, &a.row_end, rank_);
+        a.halo = halo_;
+    }
+    int rc = alloc_buffer(a, &a.buf);
+    if (rc) return rc;
+    if (zero) {
+        rc = cuda_fail(cudaMemsetAsync(a.buf.alloc, 0, a.buf.bytes, stream_), "memset");
+        if (rc) return rc;
+    }
+    auto ins = arrays_.emplace(name, a);
+    if (out) *out = &ins.first->second;
+    return CN_OK;
+}
+
+int Context::ensure_shadow(Array* a) {
+    if (a->shadow.alloc) return CN_OK;
+    return alloc_buffer(*a, &a->shadow);
+}
+
+int Context::check_leaf(const Array* a, int ndims, const int64_t* shape, const char* what) {
+    if (a->ndims != ndims) return fail(CN_ERR_SHAPE_MISMATCH, std::string(what) + ": rank differs from the stored array");
+    for (int d = 0; d < ndims; ++d)
+        if (a->shape[d] != shape[d])
+            return fail(CN_ERR_SHAPE_MISMATCH, std::string(what) + ": shape differs from the stored array");
+    return CN_OK;
+}
+
+int Context::delete_array(int name) {
+    Array* a = find(name);
+    if (!a) return fail(CN_ERR_UNKNOWN_ARRAY, "delete_array: unknown array " + std::to_string(name));
+    free_buffer(&a->buf);
+    free_buffer(&a->shadow);
+    arrays_.erase(name);
+    return CN_OK;
+}
+
+int Context::array_info(int name, int* ndims, int64_t* shape, int* dtype, int64_t* row_begin,
+                        int64_t* row_end) {
+    Array* a = find(name);
+    if (!a) return fail(CN_ERR_UNKNOWN_ARRAY, "unknown array " + std::to_string(name));
+    if (ndims) *ndims = a->ndims;
+    if (shape)
+        for (int d = 0; d < a->ndims; ++d) shape[d] = a->shape[d];
+    if (dtype) *dtype = a->dtype;
+    if (row_begin) *row_begin = a->row_begin;
+    if (row_end) *row_end = a->row_end;
+    return CN_OK;
+}
+
+// ---- communication ----------------------------------------------------------------------
+
+int Context::comm_init_id(const char id[128]) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    if (nranks_ == 1) return CN_OK;
+    cudaSetDevice(device_);
+    return comm_init(&comm_, id, rank_, nranks_, &err_);
+}
+
+int Context::mark_rank_failed(int r) {
+    if (r < 0 || r >= nranks_) return fail(CN_ERR_INVALID_ARGUMENT, "rank out of range");
+    failed_[r] = true;
+    return CN_OK;
+}
+
+int Context::exchange_halo(Array* a) {
+    if (nranks_ == 1 || a->replicated || a->halo_valid) return CN_OK;
+    if (!comm_.ready) return fail(CN_ERR_COMM, "halo exchange needs cn_comm_init first");
+    const int H = a->halo;
+    const int64_t nl = a->local_rows();
+    int64_t nb, ne, pb, pe;
+    bool has_prev = false, has_next = false;
+    if (nl > 0 && rank_ > 0) {
+        partition(a->shape[0], &pb, &pe, rank_ - 1);
+        has_prev = pe > pb;
+        if (has_prev && (pe - pb < H || nl < H))
+            return fail(CN_ERR_UNSUPPORTED, "a slab is thinner than the halo depth");
+    }
+    if (nl > 0 && rank_ + 1 < nranks_) {
+        partition(a->shape[0], &nb, &ne, rank_ + 1);
+        has_next = ne > nb;
+        if (has_next && (ne - nb < H || nl < H))
+            return fail(CN_ERR_UNSUPPORTED, "a slab is thinner than the halo depth");
+    }
+    const int64_t cnt = (int64_t)H * a->unit;
+    const size_t esz = dtype_size(a->dtype);
+    int rc;
+    if ((rc = comm_group_start(&err_))) return rc;
+    if (has_prev) {
+        if ((rc = comm_send(&comm_, a->buf.data, cnt, a->dtype, rank_ - 1, stream_, &err_))) return rc;
+        if ((rc = comm_recv(&comm_, a->buf.data - cnt * esz, cnt, a->dtype, rank_ - 1, stream_, &err_))) return rc;
+    }
+    if (has_next) {
+        if ((rc = comm_send(&comm_, a->buf.data + (nl * a->unit - cnt) * esz, cnt, a->dtype, rank_ + 1, stream_, &err_))) return rc;
+        if ((rc = comm_recv(&comm_, a->buf.data + nl * a->unit * esz, cnt, a->dtype, rank_ + 1, stream_, &err_))) return rc;
+    }
+    if ((rc = comm_group_end(&err_))) return rc;
+    a->halo_valid = true;
+    stats_.halo_exchanges++;
+    return CN_OK;
+}
+
+int Context::ensure_scratch(size_t bytes) {
+    if (scratch_bytes_ >= bytes) return CN_OK;
+    if (scratch_) {
+        cudaStreamSynchronize(stream_);
+        cudaFree(scratch_);
+        scratch_ = nullptr;
+        scratch_bytes_ = 0;
+    }
+    int rc = cuda_fail(cudaMalloc(&scratch_, bytes), "scratch allocation");
+    if (rc) return rc;
+    scratch_bytes_ = bytes;
+    return CN_OK;
+}
+
+// ---- DAG execution ----------------------------------------------------------------------
+
+int Context::receive_dag(int epoch, int64_t size, const char* msg) {
+    (void)epoch;
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    for (int r = 0; r < nranks_; ++r)
+        if (failed_[r]) return fail(CN_ERR_RANK_FAILED, "rank " + std::to_string(r) + " was marked failed");
+    cudaSetDevice(device_);
+    Dag dag;
+    int rc = parse_dag(msg, size, &dag, &err_);
+    if (rc) return rc;
+    size_t i = 0;
+    while (i < dag.nodes.size()) {
+        rc = execute_node(dag, &i);
+        if (rc) return rc;
+    }
+    for (int name : dag.deletes)
+        if (find(name)) delete_array(name);
+    return CN_OK;
+}
+
+static bool is_group_node(const DagNode& n) {
+    if (n.roots.empty()) return false;
+    bool any = false;
+    for (auto& r : n.roots) {
+        int op = r->opcode;
+        if (op == OP_NOOP) continue;
+        if (is_elementwise(op) || op == OP_SET_REGION || op == OP_COPY) any = true;
+        else if ((op == OP_SUM || op == OP_REDUCE) && n.fusible && n.roots.size() > 1)
+            continue;  // terminal reduction inside a fusible group
+        else return false;
+    }
+    return any;
+}
+
+int Context::execute_node(const Dag& dag, size_t* index) {
+    const DagNode& node = dag.nodes[*index];
+    stats_.nodes++;
+    if (node.roots.empty()) {
+        ++*index;
+        return CN_OK;
+    }
+    if (is_group_node(node)) {
+        bool done = false;
+        int rc = try_plain_fill(node, &done);
+        if (rc) return rc;
+        if (done) {
+            ++*index;
+            return CN_OK;
+        }
+        // REDUCE / SUM nodes that directly follow may be folded into this group's kernel
+        std::vector<const AstNode*> fused;
+        size_t j = *index + 1;
+        if (fuse_reductions_) {
+            while (j < dag.nodes.size() && (int)fused.size() < CN_MAX_RED) {
+                const DagNode& nx = dag.nodes[j];
+                if (nx.roots.size() != 1) break;
+                const AstNode* r = nx.roots[0].get();
+                if (r->opcode != OP_REDUCE && r->opcode != OP_SUM) break;
+                bool ok = true;
+                for (auto& op : r->operands)
+                    if (op.is_ref || !op.leaf || op.leaf->is_scalar) ok = false;
+                if (!ok) break;
+                fused.push_back(r);
+                ++j;
+            }
+        }
+        if (!fused.empty()) {
+            GroupIR probe;
+            std::string perr;
+            int lrc = lower_group(node, fused, &probe, &perr);
+            bool related = false;
+            if (lrc == CN_OK && probe.cls == GroupIR::SHIFTED) {
+                // only worth fusing when a reduction operand is produced or read by the group
+                for (auto& rd : probe.reds)
+                    for (const ValRef* v : {&rd.a, &rd.b}) {
+                        if (v->kind == ValRef::OUTVAL || v->kind == ValRef::ROOT) related = true;
+                        if (v->kind == ValRef::LEAF)
+                            for (auto& l : probe.leaves)
+                                if (&l != &probe.leaves[v->idx] && l.name == probe.leaves[v->idx].name)
+                                    related = true;
+                    }
+            }
+            if (lrc != CN_OK || probe.cls != GroupIR::SHIFTED || !related) {
+                fused.clear();
+                j = *index + 1;
+            }
+        }
+        int rc2 = execute_group(node, fused);
+        if (rc2) return rc2;
+        stats_.fused_reductions += (long long)fused.size();
+        stats_.nodes += (long long)fused.size();
+        *index = j;
+        return CN_OK;
+    }
+    ++*index;
+    int last = CN_OK;
+    for (auto& r : node.roots) {
+        switch (r->opcode) {
+            case OP_NOOP: break;
+            case OP_CREATE: last = execute_create(*r); break;
+            case OP_REDUCE:
+            case OP_SUM: last = execute_reduce(*r); break;
+            case OP_MATMUL: last = execute_matmul(*r); break;
+            case OP_RANDU: last = execute_randu(*r); break;
+            case OP_MATMATMUL:
+            case OP_TILE:
+            case OP_DIAG:
+            case OP_GET_REGION:
+                return fail(CN_ERR_UNSUPPORTED, "opcode " + std::to_string(r->opcode) +
+                                                    " is outside this backend's scope");
+            default:
+                return fail(CN_ERR_BAD_OPCODE, "unknown opcode " + std::to_string(r->opcode));
+        }
+        if (last) return last;
+    }
+    return CN_OK;
+}
+
+int Context::execute_create(const AstNode& r) {
+    if (r.ndims < 1) return fail(CN_ERR_INVALID_ARGUMENT, "CREATE without a shape");
+    return create_array(r.result_name, r.ndims, r.shape, r.dtype, true, nullptr);
+}
+
+// A group that is nothing but SET_REGION(target, literal) nodes needs no generated kernel
+// (the reference routes these to its interpreter too, src/execute_node.cpp:108-110).
+int Context::try_plain_fill(const DagNode& node, bool* done) {
+    *done = false;
+    for (auto& r : node.roots) {
+        if (r->opcode != OP_SET_REGION || r->operands.size() != 2) return CN_OK;
+        const Operand& rhs = r->operands[1];
+        if (rhs.is_ref || !rhs.leaf || !rhs.leaf->is_scalar) return CN_OK;
+        if (!r->operands[0].leaf) return CN_OK;
+    }
+    for (auto& r : node.roots) {
+        const AstNode* t = r->operands[0].leaf.get();
+        Array* a = find(t->result_name);
+        if (!a) return fail(CN_ERR_UNKNOWN_ARRAY, "SET_REGION target " + std::to_string(t->result_name) + " does not exist");
+        int rc = check_leaf(a, t->ndims, t->shape, "SET_REGION target");
+        if (rc) return rc;
+        Region reg = r->region.is_global ? Region::full(a->ndims, a->shape) : r->region;
+        if (reg.ndims != a->ndims) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION region rank differs from target");
+        for (int d = 0; d < a->ndims; ++d)
+            if (reg.stop[d] > a->shape[d]) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION region outside its target");
+        // rows of the region that live on this rank
+        int64_t s0 = reg.start[0], st0 = reg.step[0];
+        int64_t first = s0;
+        if (first < a->row_begin) first = s0 + (a->row_begin - s0 + st0 - 1) / st0 * st0;
+        int64_t stop0 = std::min<int64_t>(reg.stop[0], a->row_end);
+        int64_t n0 = first < stop0 ? (stop0 - first + st0 - 1) / st0 : 0;
+        StridedView v;
+        int64_t ext[3] = {1, 1, 1};
+        int64_t strides[3] = {0, 0, 0};
+        strides[a->ndims - 1] = 1;
+        for (int d = a->ndims - 2; d >= 0; --d) strides[d] = strides[d + 1] * a->shape[d + 1];
+        // iteration dims are right-aligned into 3 slots
+        int shift = 3 - a->ndims;
+        v.off = (first - a->row_begin) * strides[0];
+        for (int d = 0; d < a->ndims; ++d) {
+            ext[shift + d] = d == 0 ? n0 : reg.extent(d);
+            v.str[shift + d] = reg.step[d] * strides[d];
+            if (d > 0) v.off += reg.start[d] * strides[d];
+        }
+        if (n0 > 0 && ext[1] > 0 && ext[2] > 0 && ext[0] > 0) {
+            rc = cuda_fail(launch_fill_region(a->buf.data, a->dtype, v, ext, r->operands[1].leaf->scalar, stream_), "fill");
+            if (rc) return rc;
+            stats_.kernel_launches++;
+        }
+        a->halo_valid = false;
+    }
+    *done = true;
+    return CN_OK;
+}
+
+}  // namespace cn

@@ -1,0 +1,179 @@
+// The per-GPU execution context: array table, slab partition, DAG executor, kernel cache.
+//
+// One context = one rank = one GPU.  It takes the place of the reference's
+// ArrayDAGGroup + PartitionImpl<N> + ArrayDAGExecutorND<N> trio (src/backend.hpp:239-582):
+// instead of over-decomposed chare tiles there is exactly one slab per array per GPU,
+// split along dimension 0, with `halo` extra rows (planes) on each side when more than
+// one rank takes part.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "cn_device.cuh"
+#include "cn_types.hpp"
+#include "comm.hpp"
+#include "group_ir.hpp"
+#include "jit.hpp"
+
+namespace cn {
+
+struct Buffer {
+    void* alloc = nullptr;  // start of the allocation
+    char* data = nullptr;   // address of local element (0,0,0)
+    size_t bytes = 0;
+};
+
+struct Array {
+    int name = -1;
+    int ndims = 0;
+    int64_t shape[kMaxDims] = {0, 0, 0};
+    int dtype = DT_F64;
+    bool replicated = false;  // size-1 arrays live on every rank
+    int64_t row_begin = 0, row_end = 0;  // local range of dimension 0
+    int64_t unit = 1;                    // elements per index of dimension 0
+    int halo = 0;                        // halo rows allocated on each side
+    Buffer buf, shadow;
+    bool halo_valid = false;
+
+    int64_t local_rows() const { return row_end - row_begin; }
+    int64_t local_elems() const { return local_rows() * unit; }
+    int64_t global_elems() const {
+        int64_t n = 1;
+        for (int d = 0; d < ndims; ++d) n *= shape[d];
+        return n;
+    }
+};
+
+struct CompiledGroup {
+    CUmodule module = nullptr;
+    CUfunction func = nullptr;
+    int blocks_per_sm = 1;  // resident 256-thread blocks per SM, from the occupancy query
+    std::string source;
+    std::string log;
+};
+
+struct Stats {
+    long long kernel_launches = 0;   // kernels of this library launched (AOT + generated)
+    long long group_launches = 0;    // of which generated group kernels
+    long long compiles = 0;          // NVRTC compilations (cache misses)
+    long long halo_exchanges = 0;
+    long long allreduces = 0;
+    long long fused_reductions = 0;  // REDUCE/SUM nodes folded into a group kernel
+    long long nodes = 0;             // DAG nodes executed
+    long long bytes_h2d = 0, bytes_d2h = 0;
+};
+
+struct DriverApi {
+    CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*ModuleUnload)(CUmodule) = nullptr;
+    CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                             unsigned, CUstream, void**, void**) = nullptr;
+    CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
+};
+
+class Context {
+public:
+    Context(int device, int rank, int nranks);
+    ~Context();
+    int init();  // binds the device, creates streams and scratch; CN_ERR_NO_DEVICE without a GPU
+
+    // ---- boundary entry points (see include/cnb200.h) ----
+    int comm_init_id(const char id[128]);
+    int receive_dag(int epoch, int64_t size, const char* msg);
+    int get(int name, int64_t count, int dtype, void* out);
+    int get_local(int name, int64_t* row_begin, int64_t* row_end, int64_t capacity, void* out);
+    int put(int name, int ndims, const int64_t* shape, int dtype, const void* host);
+    int delete_array(int name);
+    int synchronize();
+    int compile_group(const char* blob, int64_t size, uint64_t* handle);
+    int group_source(uint64_t handle, const char** src);
+    int launch_group(uint64_t handle, int n_in, void* const* in_ptrs, const int64_t* in_off,
+                     const int64_t* in_str, int n_bc, void* const* bc_ptrs, int n_out,
+                     void* const* out_ptrs, const int64_t* out_off, const int64_t* out_str,
+                     const int64_t* ext);
+    int timer_start();
+    int timer_stop(float* ms);
+    int mark_rank_failed(int r);
+    int array_info(int name, int* ndims, int64_t* shape, int* dtype, int64_t* row_begin,
+                   int64_t* row_end);
+
+    const std::string& last_error() const { return err_; }
+    const Stats& stats() const { return stats_; }
+    int rank() const { return rank_; }
+    int nranks() const { return nranks_; }
+    void set_halo(int h) { halo_ = h; }
+    void set_fuse_reductions(bool f) { fuse_reductions_ = f; }
+    void set_tile(int tx, int r) {
+        if (tx > 0) tile_.tx = tx;
+        if (r > 0) tile_.r = r;
+    }
+
+private:
+    int fail(int code, const std::string& msg);
+    int cuda_fail(cudaError_t e, const char* what);
+    int driver_fail(CUresult r, const char* what);
+
+    // arrays
+    Array* find(int name);
+    int create_array(int name, int ndims, const int64_t* shape, int dtype, bool zero, Array** out);
+    int alloc_buffer(const Array& a, Buffer* b);
+    void free_buffer(Buffer* b);
+    int ensure_shadow(Array* a);
+    int check_leaf(const Array* a, int ndims, const int64_t* shape, const char* what);
+    void partition(int64_t n0, int64_t* begin, int64_t* end, int r) const;
+
+    // execution
+    int execute_node(const Dag& dag, size_t* index);
+    int execute_group(const DagNode& node, const std::vector<const AstNode*>& fused);
+    int run_group(const GroupIR& g);
+    int run_shifted(const GroupIR& g, CompiledGroup* k);
+    int run_strided(const GroupIR& g, CompiledGroup* k);
+    int run_scalar_only(const GroupIR& g, CompiledGroup* k);
+    int bind_scalars(const GroupIR& g, CnGroupArgs* a, std::vector<std::pair<Array*, Buffer>>* swaps);
+    int bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::vector<Array*>* results);
+    int finish_reductions(const std::vector<Array*>& results);
+    int launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block);
+    int get_kernel(const GroupIR& g, CompiledGroup** out);
+    int execute_reduce(const AstNode& root);
+    int execute_matmul(const AstNode& root);
+    int execute_randu(const AstNode& root);
+    int execute_create(const AstNode& root);
+    int try_plain_fill(const DagNode& node, bool* done);
+    int exchange_halo(Array* a);
+    int ensure_scratch(size_t bytes);
+    int operand_array(const Operand& op, Array** out, Region* region);
+
+    int device_, rank_, nranks_;
+    int halo_ = 1;
+    bool fuse_reductions_ = true;
+    bool initialised_ = false;
+    int sm_count_ = 148;
+    cudaStream_t stream_ = nullptr;
+    cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
+    Comm comm_;
+    std::vector<bool> failed_;
+    DriverApi drv_;
+    TileConfig tile_;
+
+    std::unordered_map<int, Array> arrays_;
+    std::unordered_map<std::string, CompiledGroup> kernels_;
+    std::vector<std::pair<std::string, GroupIR>> handles_;  // cn_compile_group handles
+
+    double* partials_ = nullptr;  // CN_MAX_RED * max_grid_ accumulators
+    unsigned int* counter_ = nullptr;
+    int max_grid_ = 0;
+    void* scratch_ = nullptr;  // matvec x gather / get staging
+    size_t scratch_bytes_ = 0;
+
+    std::string err_;
+    Stats stats_;
+};
+
+}  // namespace cn

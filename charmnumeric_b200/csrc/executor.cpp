@@ -1,0 +1,731 @@
+// Node execution: fused groups (generated kernels), dot / sum, matvec, seeded fill, and the
+// host-facing get / put / timer entry points.
+//
+// Reference counterparts: execute_node_nd JIT paths (src/execute_node.cpp:1195-1585),
+// execute_reduce_node (src/executor_reduce.cpp:7-119), execute_matmul_node
+// (src/executor_matmul.cpp:149-498), process_get + gather (src/partition_get.cpp:3-67,
+// src/dag_group_runtime.cpp:99-118).
+#include <algorithm>
+#include <cstring>
+
+#include "context.hpp"
+#include "kernels.hpp"
+
+namespace cn {
+
+namespace {
+
+void array_strides(const Array& a, int64_t* s) {
+    s[0] = s[1] = s[2] = 0;
+    s[a.ndims - 1] = 1;
+    for (int d = a.ndims - 2; d >= 0; --d) s[d] = s[d + 1] * a.shape[d + 1];
+}
+
+}  // namespace
+
+int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
+    std::string key = g.key() + "|T" + std::to_string(tile_.tx) + "," + std::to_string(tile_.r);
+    auto it = kernels_.find(key);
+    if (it != kernels_.end()) {
+        *out = &it->second;
+        return CN_OK;
+    }
+    CompiledGroup k;
+    int rc = generate_source(g, &k.source, &err_);
+    if (rc) return rc;
+    std::vector<char> cubin;
+    rc = nvrtc_compile(k.source, tile_, &cubin, &k.log);
+    if (rc) return fail(rc, "group kernel failed to compile:\n" + k.log);
+    stats_.compiles++;
+    if ((rc = driver_fail(drv_.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData"))) return rc;
+    if ((rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, "cn_group"), "cuModuleGetFunction"))) return rc;
+    int occ = 0;
+    if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, CN_BLOCK, 0) == CUDA_SUCCESS && occ > 0)
+        k.blocks_per_sm = occ;
+    auto ins = kernels_.emplace(key, std::move(k));
+    *out = &ins.first->second;
+    return CN_OK;
+}
+
+int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block) {
+    void* params[] = {(void*)&a};
+    int rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, 0,
+                                           (CUstream)stream_, params, nullptr),
+                         "cuLaunchKernel");
+    if (rc) return rc;
+    stats_.kernel_launches++;
+    stats_.group_launches++;
+    return CN_OK;
+}
+
+int Context::execute_group(const DagNode& node, const std::vector<const AstNode*>& fused) {
+    GroupIR g;
+    int rc = lower_group(node, fused, &g, &err_);
+    if (rc) return rc;
+    return run_group(g);
+}
+
+int Context::run_group(const GroupIR& g) {
+    CompiledGroup* k = nullptr;
+    int rc = get_kernel(g, &k);
+    if (rc) return rc;
+    switch (g.cls) {
+        case GroupIR::SCALAR_ONLY: return run_scalar_only(g, k);
+        case GroupIR::SHIFTED: return run_shifted(g, k);
+        case GroupIR::STRIDED: return run_strided(g, k);
+    }
+    return fail(CN_ERR_UNSUPPORTED, "unknown group class");
+}
+
+// Size-1 inputs and outputs.  An output whose array is also read as an input of the same
+// launch gets a fresh buffer (other blocks may still be reading the old one).
+int Context::bind_scalars(const GroupIR& g, CnGroupArgs* a,
+                          std::vector<std::pair<Array*, Buffer>>* swaps) {
+    for (size_t i = 0; i < g.scalars.size(); ++i) a->sc[i] = g.scalars[i];
+    for (size_t i = 0; i < g.bcast_names.size(); ++i) {
+        Array* s = find(g.bcast_names[i]);
+        if (!s) return fail(CN_ERR_UNKNOWN_ARRAY, "size-1 array " + std::to_string(g.bcast_names[i]) + " does not exist");
+        if (s->global_elems() != 1) return fail(CN_ERR_SHAPE_MISMATCH, "broadcast operand is not a size-1 array");
+        if (s->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "size-1 operand dtype differs from the group dtype");
+        a->bc[i] = s->buf.data;
+    }
+    for (size_t i = 0; i < g.souts.size(); ++i) {
+        const ScalarOutIR& so = g.souts[i];
+        Array* s = find(so.name);
+        if (!s) {
+            if (so.is_set) return fail(CN_ERR_UNKNOWN_ARRAY, "SET_REGION target " + std::to_string(so.name) + " does not exist");
+            int64_t one[1] = {1};
+            int rc = create_array(so.name, 1, one, g.dtype, false, &s);
+            if (rc) return rc;
+        }
+        if (s->global_elems() != 1) return fail(CN_ERR_SHAPE_MISMATCH, "scalar result stored into a larger array");
+        if (s->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "scalar result dtype differs from the group dtype");
+        bool read_too = std::find(g.bcast_names.begin(), g.bcast_names.end(), so.name) != g.bcast_names.end();
+        if (read_too && g.cls != GroupIR::SCALAR_ONLY) {
+            Buffer nb;
+            int rc = alloc_buffer(*s, &nb);
+            if (rc) return rc;
+            a->sout[i] = nb.data;
+            swaps->push_back({s, nb});
+        } else {
+            a->sout[i] = s->buf.data;
+        }
+    }
+    return CN_OK;
+}
+
+int Context::bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::vector<Array*>* results) {
+    if (g.reds.empty()) return CN_OK;
+    if (grid > max_grid_) return fail(CN_ERR_LIMIT, "grid larger than the reduction scratch");
+    a->partials = partials_;
+    a->counter = counter_;
+    for (size_t q = 0; q < g.reds.size(); ++q) {
+        Array* r = nullptr;
+        int64_t one[1] = {1};
+        int rc = create_array(g.reds[q].result_name, 1, one, g.dtype, false, &r);
+        if (rc) return rc;
+        a->red[q] = r->buf.data;
+        results->push_back(r);
+    }
+    return CN_OK;
+}
+
+int Context::finish_reductions(const std::vector<Array*>& results) {
+    if (nranks_ == 1) return CN_OK;
+    if (!comm_.ready && !results.empty()) return fail(CN_ERR_COMM, "reduction across ranks needs cn_comm_init first");
+    for (Array* r : results) {
+        int rc = comm_allreduce_sum(&comm_, r->buf.data, 1, r->dtype, stream_, &err_);
+        if (rc) return rc;
+        stats_.allreduces++;
+    }
+    return CN_OK;
+}
+
+int Context::run_scalar_only(const GroupIR& g, CompiledGroup* k) {
+    CnGroupArgs a;
+    memset(&a, 0, sizeof(a));
+    std::vector<std::pair<Array*, Buffer>> swaps;
+    int rc = bind_scalars(g, &a, &swaps);
+    if (rc) return rc;
+    return launch(k, a, 1, 32);
+}
+
+int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
+    const int nd = g.ndims;
+    CnGroupArgs a;
+    memset(&a, 0, sizeof(a));
+    std::vector<std::pair<Array*, Buffer>> swaps;
+    int rc = bind_scalars(g, &a, &swaps);
+    if (rc) return rc;
+
+    // inputs
+    std::vector<int> in_names = g.input_arrays();
+    if ((int)in_names.size() > CN_MAX_IN) return fail(CN_ERR_LIMIT, "too many input arrays in one group");
+    Array* ref = nullptr;
+    std::vector<Array*> ins;
+    for (size_t i = 0; i < in_names.size(); ++i) {
+        Array* x = find(in_names[i]);
+        if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "operand array " + std::to_string(in_names[i]) + " does not exist");
+        if ((rc = check_leaf(x, nd, g.array_shape, "group operand"))) return rc;
+        if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "operand dtype differs from the group dtype");
+        ins.push_back(x);
+        ref = x;
+    }
+    // outputs
+    std::vector<Array*> outs;
+    for (size_t m = 0; m < g.outs.size(); ++m) {
+        const OutIR& o = g.outs[m];
+        Array* x = find(o.name);
+        if (o.is_set) {
+            if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "SET_REGION target " + std::to_string(o.name) + " does not exist");
+            if ((rc = check_leaf(x, nd, g.array_shape, "SET_REGION target"))) return rc;
+            if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "target dtype differs from the group dtype");
+        } else {
+            if ((rc = create_array(o.name, nd, g.array_shape, g.dtype, false, &x))) return rc;
+            // create_array may have re-hashed the table: refresh the input pointers
+            for (size_t i = 0; i < in_names.size(); ++i) ins[i] = find(in_names[i]);
+            for (size_t j = 0; j < outs.size(); ++j) outs[j] = find(g.outs[j].name);
+        }
+        outs.push_back(x);
+        ref = x;
+    }
+    if (!ref) return fail(CN_ERR_UNSUPPORTED, "group touches no array");
+
+    // halos: a leaf shifted along dimension 0 reads rows owned by a neighbour
+    if (nranks_ > 1 && !ref->replicated) {
+        if (g.max_halo > halo_) return fail(CN_ERR_UNSUPPORTED, "stencil reaches further along dimension 0 than the halo depth");
+        for (auto& l : g.leaves)
+            if (l.delta[0] != 0) {
+                Array* x = find(l.name);
+                if ((rc = exchange_halo(x))) return rc;
+            }
+    }
+
+    for (size_t i = 0; i < ins.size(); ++i) a.in[i] = ins[i]->buf.data;
+    for (size_t m = 0; m < outs.size(); ++m) {
+        Array* x = outs[m];
+        a.old[m] = x->buf.data;
+        if (g.copy_through && g.outs[m].hazard) {
+            if ((rc = ensure_shadow(x))) return rc;
+            a.out[m] = x->shadow.data;
+        } else {
+            a.out[m] = x->buf.data;
+        }
+    }
+
+    // iteration box in local coordinates
+    const int64_t rb = ref->row_begin, re = ref->row_end;
+    int64_t lo[3] = {0, 0, 0}, hi[3] = {0, 0, 0}, rlo[3] = {0, 0, 0}, rhi[3] = {0, 0, 0};
+    for (int d = 0; d < nd; ++d) {
+        lo[d] = g.box_lo[d];
+        hi[d] = g.box_hi[d];
+        rlo[d] = g.reg_lo[d];
+        rhi[d] = g.reg_hi[d];
+    }
+    lo[0] = std::max(lo[0], rb) - rb;
+    hi[0] = std::min(hi[0], re) - rb;
+    rlo[0] = std::max(rlo[0], rb) - rb;
+    rhi[0] = std::min(rhi[0], re) - rb;
+    bool empty = false;
+    for (int d = 0; d < nd; ++d)
+        if (hi[d] <= lo[d]) empty = true;
+
+    int64_t strides[3];
+    array_strides(*ref, strides);
+    const int V = g.vec;
+    int64_t ntiles = 0;
+    if (g.flat) {
+        int64_t n = ref->local_elems();
+        a.lo[0] = 0;
+        a.hi[0] = n;
+        a.rlo[0] = 0;
+        a.rhi[0] = n;
+        int64_t per = (int64_t)tile_.r * CN_BLOCK * V;
+        ntiles = (n + per - 1) / per;
+    } else {
+        for (int d = 0; d < nd; ++d) {
+            a.lo[d] = lo[d];
+            a.hi[d] = hi[d];
+            a.rlo[d] = rlo[d];
+            a.rhi[d] = rhi[d];
+        }
+        a.stride[0] = strides[0];
+        a.stride[1] = strides[1];
+        a.stride[2] = strides[2];
+        if (!empty) {
+            const int L = nd - 1;
+            int64_t xbase = V == 2 ? (lo[L] & ~1LL) : lo[L];
+            if (nd == 1) {
+                int64_t per = (int64_t)tile_.r * CN_BLOCK * V;
+                ntiles = (hi[0] - xbase + per - 1) / per;
+            } else {
+                int64_t ntx = (hi[L] - xbase + (int64_t)tile_.tx * V - 1) / ((int64_t)tile_.tx * V);
+                int64_t rows_per = (int64_t)(CN_BLOCK / tile_.tx) * tile_.r;
+                int64_t nty = (hi[nd - 2] - lo[nd - 2] + rows_per - 1) / rows_per;
+                int64_t nz = nd == 3 ? hi[0] - lo[0] : 1;
+                a.ntx = ntx;
+                a.nty = nty;
+                ntiles = ntx * nty * nz;
+            }
+        }
+    }
+    if (ntiles >= (1LL << 31)) return fail(CN_ERR_LIMIT, "too many tiles for one launch");
+    a.ntiles = ntiles;
+    int grid = (int)std::min<int64_t>(std::max<int64_t>(ntiles, 1), (int64_t)sm_count_ * k->blocks_per_sm);
+
+    std::vector<Array*> results;
+    if ((rc = bind_reductions(g, &a, grid, &results))) return rc;
+    // binding may have created arrays: the table can re-hash, so refresh raw pointers
+    if (!results.empty()) {
+        for (size_t q = 0; q < results.size(); ++q) {
+            results[q] = find(g.reds[q].result_name);
+            a.red[q] = results[q]->buf.data;
+        }
+        for (size_t m = 0; m < outs.size(); ++m) outs[m] = find(g.outs[m].name);
+    }
+
+    if (ntiles > 0 || !g.reds.empty() || !g.souts.empty()) {
+        if ((rc = launch(k, a, grid, CN_BLOCK))) return rc;
+    }
+    for (size_t m = 0; m < outs.size(); ++m) {
+        Array* x = outs[m];
+        if (g.copy_through && g.outs[m].hazard) std::swap(x->buf, x->shadow);
+        x->halo_valid = false;
+    }
+    for (auto& sw : swaps) {
+        free_buffer(&sw.first->buf);
+        sw.first->buf = sw.second;
+    }
+    return finish_reductions(results);
+}
+
+int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
+    const int nd = g.ndims;
+    CnGroupArgs a;
+    memset(&a, 0, sizeof(a));
+    std::vector<std::pair<Array*, Buffer>> swaps;
+    int rc = bind_scalars(g, &a, &swaps);
+    if (rc) return rc;
+    if ((int)g.leaves.size() > CN_MAX_IN) return fail(CN_ERR_LIMIT, "too many operands in one group");
+
+    // Along dimension 0 every view must walk the slab in step with the output, otherwise
+    // rows would have to move between ranks.
+    int64_t it_lo = 0, it_hi = g.extent[0];  // iteration rows executed on this rank
+    if (nranks_ > 1) {
+        const Region* r0 = nullptr;
+        int64_t n0 = -1;
+        auto check = [&](const Region& r, int64_t shape0) {
+            if (r.step[0] != 1) return false;
+            if (!r0) {
+                r0 = &r;
+                n0 = shape0;
+                return true;
+            }
+            return r.start[0] == r0->start[0] && shape0 == n0;
+        };
+        bool ok = true;
+        for (auto& l : g.leaves) ok = ok && check(l.region, l.shape[0]);
+        for (auto& o : g.outs) ok = ok && check(o.region, o.shape[0]);
+        if (!ok)
+            return fail(CN_ERR_UNSUPPORTED,
+                        "a strided group whose views are offset against each other along "
+                        "dimension 0 needs a single rank");
+        if (r0) {
+            int64_t b, e;
+            partition(n0, &b, &e, rank_);
+            it_lo = std::max<int64_t>(0, b - r0->start[0]);
+            it_hi = std::min<int64_t>(g.extent[0], e - r0->start[0]);
+            if (it_hi < it_lo) it_hi = it_lo;
+        }
+    }
+
+    auto bind_view = [&](const Array& x, const Region& r, long long* off, long long* str) {
+        int64_t s[3];
+        array_strides(x, s);
+        *off = (r.start[0] + it_lo - x.row_begin) * s[0];
+        for (int d = 1; d < nd; ++d) *off += r.start[d] * s[d];
+        for (int d = 0; d < nd; ++d) str[d] = r.step[d] * s[d];
+    };
+    for (size_t i = 0; i < g.leaves.size(); ++i) {
+        const LeafIR& l = g.leaves[i];
+        Array* x = find(l.name);
+        if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "operand array " + std::to_string(l.name) + " does not exist");
+        if ((rc = check_leaf(x, l.ndims, l.shape, "group operand"))) return rc;
+        if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "operand dtype differs from the group dtype");
+        a.in[i] = x->buf.data;
+        bind_view(*x, l.region, &a.in_off[i], a.in_str[i]);
+    }
+    struct Pending {
+        Array* target;
+        Buffer temp;
+        Region region;
+    };
+    std::vector<Pending> copy_back;
+    int64_t ext[3] = {1, 1, 1};
+    for (int d = 0; d < nd; ++d) ext[d] = g.extent[d];
+    ext[0] = it_hi - it_lo;
+    for (size_t m = 0; m < g.outs.size(); ++m) {
+        const OutIR& o = g.outs[m];
+        Array* x = find(o.name);
+        if (o.is_set) {
+            if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "SET_REGION target " + std::to_string(o.name) + " does not exist");
+            if ((rc = check_leaf(x, o.ndims, o.shape, "SET_REGION target"))) return rc;
+            if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "target dtype differs from the group dtype");
+        } else {
+            if ((rc = create_array(o.name, o.ndims, o.shape, g.dtype, false, &x))) return rc;
+            for (size_t i = 0; i < g.leaves.size(); ++i) a.in[i] = find(g.leaves[i].name)->buf.data;
+        }
+        if (o.hazard) {
+            // right-hand side reads the target elsewhere: evaluate into a dense temporary
+            // first, then copy (what the reference always does, src/execute_node.cpp:1581-1584)
+            Pending p;
+            p.target = x;
+            p.region = o.region;
+            size_t bytes = (size_t)std::max<int64_t>(1, ext[0] * (nd > 1 ? ext[1] : 1) * (nd > 2 ? ext[2] : 1)) * dtype_size(g.dtype);
+            void* t = nullptr;
+            if ((rc = cuda_fail(cudaMallocAsync(&t, bytes + 256, stream_), "temporary"))) return rc;
+            p.temp.alloc = t;
+            p.temp.data = (char*)t;
+            p.temp.bytes = bytes;
+            a.out[m] = t;
+            a.out_off[m] = 0;
+            int64_t s = 1;
+            for (int d = nd - 1; d >= 0; --d) {
+                a.out_str[m][d] = s;
+                s *= ext[d];
+            }
+            copy_back.push_back(p);
+        } else {
+            a.out[m] = x->buf.data;
+            bind_view(*x, o.region, &a.out_off[m], a.out_str[m]);
+        }
+        x->halo_valid = false;
+    }
+    for (int d = 0; d < 3; ++d) a.ext[d] = d < nd ? ext[d] : 1;
+    int64_t total = 1;
+    for (int d = 0; d < nd; ++d) total *= ext[d];
+    int grid = (int)std::min<int64_t>(std::max<int64_t>((total + CN_BLOCK - 1) / CN_BLOCK, 1), (int64_t)sm_count_ * k->blocks_per_sm);
+    std::vector<Array*> results;
+    if ((rc = bind_reductions(g, &a, grid, &results))) return rc;
+    for (size_t q = 0; q < results.size(); ++q) {
+        results[q] = find(g.reds[q].result_name);
+        a.red[q] = results[q]->buf.data;
+    }
+    if (total > 0 || !g.reds.empty() || !g.souts.empty())
+        if ((rc = launch(k, a, grid, CN_BLOCK))) return rc;
+    for (auto& p : copy_back) {
+        Array* x = find(p.target->name);
+        StridedView dv, sv;
+        int64_t e3[3] = {1, 1, 1};
+        int64_t s[3];
+        array_strides(*x, s);
+        const int shift = 3 - nd;
+        dv.off = (p.region.start[0] + it_lo - x->row_begin) * s[0];
+        for (int d = 1; d < nd; ++d) dv.off += p.region.start[d] * s[d];
+        int64_t dense = 1;
+        for (int d = nd - 1; d >= 0; --d) {
+            e3[shift + d] = ext[d];
+            dv.str[shift + d] = p.region.step[d] * s[d];
+            sv.str[shift + d] = dense;
+            dense *= ext[d];
+        }
+        if (total > 0) {
+            if ((rc = cuda_fail(launch_copy_region(x->buf.data, dv, p.temp.data, sv, e3, g.dtype, stream_), "copy back"))) return rc;
+            stats_.kernel_launches++;
+        }
+        cudaFreeAsync(p.temp.alloc, stream_);
+    }
+    for (auto& sw : swaps) {
+        free_buffer(&sw.first->buf);
+        sw.first->buf = sw.second;
+    }
+    return finish_reductions(results);
+}
+
+// ---- non-fusible nodes --------------------------------------------------------------------
+
+int Context::operand_array(const Operand& op, Array** out, Region* region) {
+    if (op.is_ref || !op.leaf) return fail(CN_ERR_BAD_BLOB, "operand must name an array");
+    Array* x = find(op.leaf->result_name);
+    if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "operand array " + std::to_string(op.leaf->result_name) + " does not exist");
+    *out = x;
+    *region = op.region.is_global ? Region::full(x->ndims, x->shape) : op.region;
+    if (region->ndims != x->ndims) return fail(CN_ERR_SHAPE_MISMATCH, "operand region rank differs from its array");
+    for (int d = 0; d < x->ndims; ++d)
+        if (region->stop[d] > x->shape[d] || region->start[d] > region->stop[d])
+            return fail(CN_ERR_SHAPE_MISMATCH, "operand region lies outside its array");
+    return CN_OK;
+}
+
+// dot(lhs, rhs) / sum(x) -> size-1 array.  The reference accepts 1-D operands only
+// (src/executor_reduce.cpp:9-12); any rank is accepted here as long as both operands are
+// whole arrays of one shape (an addition to the protocol).
+int Context::execute_reduce(const AstNode& r) {
+    const bool is_dot = r.opcode == OP_REDUCE;
+    if ((int)r.operands.size() != (is_dot ? 2 : 1)) return fail(CN_ERR_BAD_BLOB, "wrong operand count for a reduction");
+    Array *x = nullptr, *y = nullptr;
+    Region rx, ry;
+    int rc = operand_array(r.operands[0], &x, &rx);
+    if (rc) return rc;
+    if (is_dot && (rc = operand_array(r.operands[1], &y, &ry))) return rc;
+    auto whole = [](const Array& a, const Region& g) {
+        for (int d = 0; d < a.ndims; ++d)
+            if (g.start[d] != 0 || g.stop[d] != a.shape[d] || g.step[d] != 1) return false;
+        return true;
+    };
+    if (!whole(*x, rx) || (y && !whole(*y, ry)))
+        return fail(CN_ERR_UNSUPPORTED, "reductions over sub-regions are not supported; assign the view to an array first");
+    if (y) {
+        if (x->ndims != y->ndims) return fail(CN_ERR_SHAPE_MISMATCH, "dot operands have different ranks");
+        for (int d = 0; d < x->ndims; ++d)
+            if (x->shape[d] != y->shape[d]) return fail(CN_ERR_SHAPE_MISMATCH, "dot operands have different shapes");
+        if (x->dtype != y->dtype) return fail(CN_ERR_BAD_DTYPE, "dot operands have different dtypes");
+    }
+    const int dtype = x->dtype;
+    const int64_t n = x->local_elems();
+    const void* px = x->buf.data;
+    const void* py = y ? y->buf.data : nullptr;
+    Array* res = nullptr;
+    int64_t one[1] = {1};
+    if ((rc = create_array(r.result_name, 1, one, dtype, false, &res))) return rc;
+    int grid = dot_grid_size(n, sm_count_);
+    if (grid > max_grid_) grid = max_grid_;
+    if ((rc = cuda_fail(launch_dot(px, py, n, dtype, partials_, counter_, res->buf.data, grid, stream_), "dot"))) return rc;
+    stats_.kernel_launches++;
+    std::vector<Array*> results{res};
+    return finish_reductions(results);
+}
+
+// y = A @ x for a 2-D matrix and a 1-D vector; A is row-partitioned, x is gathered to every
+// rank, each rank multiplies its row block (no partial sums cross ranks, unlike the
+// reference's column-tile partials, src/execute_node.cpp:233-270, :550-578).
+int Context::execute_matmul(const AstNode& r) {
+    if (r.operands.size() != 2) return fail(CN_ERR_BAD_BLOB, "MATMUL needs (matrix, vector)");
+    Array *A = nullptr, *x = nullptr;
+    Region ra, rx;
+    int rc = operand_array(r.operands[0], &A, &ra);
+    if (rc) return rc;
+    if ((rc = operand_array(r.operands[1], &x, &rx))) return rc;
+    if (A->ndims != 2) return fail(CN_ERR_UNSUPPORTED, "only 2-D matrices are supported by matvec (3-D dim-drop and mat-mat are out of scope)");
+    if (x->ndims != 1) return fail(CN_ERR_UNSUPPORTED, "matvec needs a 1-D vector");
+    if (A->dtype != x->dtype) return fail(CN_ERR_BAD_DTYPE, "matvec operands have different dtypes");
+    if (!ra.unit_step() || !rx.unit_step()) return fail(CN_ERR_UNSUPPORTED, "matvec on stepped views is not supported");
+    const int64_t rows = ra.extent(0), cols = ra.extent(1);
+    if (cols != rx.extent(0)) return fail(CN_ERR_SHAPE_MISMATCH, "matrix columns differ from vector length");
+    const size_t esz = dtype_size(A->dtype);
+    const int dtype = A->dtype;
+    const int aname = A->name, xname = x->name;
+    int64_t yshape[1] = {rows};
+    Array* y = nullptr;
+    if (r.result_name == aname || r.result_name == xname) return fail(CN_ERR_HAZARD, "matvec result aliases an operand");
+    if ((rc = create_array(r.result_name, 1, yshape, dtype, false, &y))) return rc;
+    A = find(aname);
+    x = find(xname);
+    if (nranks_ == 1) {
+        const char* pa = A->buf.data + (ra.start[0] * A->shape[1] + ra.start[1]) * esz;
+        const char* px = x->buf.data + rx.start[0] * esz;
+        if ((rc = cuda_fail(launch_matvec(pa, A->shape[1], px, y->buf.data, rows, cols, dtype, stream_), "matvec"))) return rc;
+        stats_.kernel_launches++;
+        y->halo_valid = false;
+        return CN_OK;
+    }
+    // multi-rank: whole operands only, so that A's and y's row partitions coincide
+    if (ra.start[0] != 0 || ra.start[1] != 0 || rows != A->shape[0] || cols != A->shape[1] ||
+        rx.start[0] != 0 || cols != x->shape[0])
+        return fail(CN_ERR_UNSUPPORTED, "sliced matvec needs a single rank");
+    if (!comm_.ready) return fail(CN_ERR_COMM, "matvec across ranks needs cn_comm_init first");
+    if ((rc = ensure_scratch((size_t)cols * esz + 256))) return rc;
+    if ((rc = comm_group_start(&err_))) return rc;
+    for (int p = 0; p < nranks_; ++p) {
+        int64_t b, e;
+        partition(cols, &b, &e, p);
+        if (e <= b) continue;
+        if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * esz, e - b, dtype, p, stream_, &err_))) return rc;
+    }
+    if ((rc = comm_group_end(&err_))) return rc;
+    if ((rc = cuda_fail(launch_matvec(A->buf.data, A->shape[1], scratch_, y->buf.data, A->local_rows(), cols, dtype, stream_), "matvec"))) return rc;
+    stats_.kernel_launches++;
+    y->halo_valid = false;
+    return CN_OK;
+}
+
+// Seeded uniform fill (an addition: the reference's random.randn returns zeros,
+// charmnumeric/random.py:4-5).  Element with global linear index g depends on (seed, g)
+// only, so the values do not change with the number of ranks.
+int Context::execute_randu(const AstNode& r) {
+    if (r.operands.size() != 3) return fail(CN_ERR_BAD_BLOB, "RANDU needs (seed, lo, hi)");
+    double v[3];
+    for (int i = 0; i < 3; ++i) {
+        const Operand& op = r.operands[i];
+        if (op.is_ref || !op.leaf || !op.leaf->is_scalar) return fail(CN_ERR_BAD_BLOB, "RANDU operands must be literal scalars");
+        v[i] = op.leaf->scalar;
+    }
+    if (v[0] < 0 || v[0] > 9007199254740992.0) return fail(CN_ERR_INVALID_ARGUMENT, "RANDU seed must be an integer in [0, 2^53]");
+    Array* x = nullptr;
+    int rc = create_array(r.result_name, r.ndims, r.shape, r.dtype, false, &x);
+    if (rc) return rc;
+    rc = cuda_fail(launch_randu(x->buf.data, x->dtype, x->local_elems(), x->row_begin * x->unit,
+                                (uint64_t)v[0], v[1], v[2], stream_), "randu");
+    if (rc) return rc;
+    stats_.kernel_launches++;
+    x->halo_valid = false;
+    return CN_OK;
+}
+
+// ---- host-facing data movement -----------------------------------------------------------
+
+int Context::synchronize() {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    return cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+}
+
+int Context::get(int name, int64_t count, int dtype, void* out) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    cudaSetDevice(device_);
+    Array* x = find(name);
+    if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "get: unknown array " + std::to_string(name));
+    if (dtype != x->dtype) return fail(CN_ERR_BAD_DTYPE, "get: dtype differs from the stored array");
+    if (count != x->global_elems()) return fail(CN_ERR_SHAPE_MISMATCH, "get: element count differs from the stored array");
+    if (!out) return fail(CN_ERR_INVALID_ARGUMENT, "get: null output buffer");
+    const size_t esz = dtype_size(dtype);
+    int rc;
+    if (nranks_ == 1 || x->replicated) {
+        if ((rc = cuda_fail(cudaMemcpyAsync(out, x->buf.data, count * esz, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+        stats_.bytes_d2h += count * esz;
+        return synchronize();
+    }
+    if (!comm_.ready) return fail(CN_ERR_COMM, "get across ranks needs cn_comm_init first");
+    if ((rc = ensure_scratch(count * esz + 256))) return rc;
+    x = find(name);
+    if ((rc = comm_group_start(&err_))) return rc;
+    for (int p = 0; p < nranks_; ++p) {
+        int64_t b, e;
+        partition(x->shape[0], &b, &e, p);
+        if (e <= b) continue;
+        if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * x->unit * esz, (e - b) * x->unit, dtype, p, stream_, &err_))) return rc;
+    }
+    if ((rc = comm_group_end(&err_))) return rc;
+    if ((rc = cuda_fail(cudaMemcpyAsync(out, scratch_, count * esz, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+    stats_.bytes_d2h += count * esz;
+    return synchronize();
+}
+
+int Context::get_local(int name, int64_t* row_begin, int64_t* row_end, int64_t capacity, void* out) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    cudaSetDevice(device_);
+    Array* x = find(name);
+    if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "get_local: unknown array " + std::to_string(name));
+    if (row_begin) *row_begin = x->row_begin;
+    if (row_end) *row_end = x->row_end;
+    if (!out) return CN_OK;
+    if (capacity < x->local_elems()) return fail(CN_ERR_INVALID_ARGUMENT, "get_local: buffer too small");
+    const size_t bytes = (size_t)x->local_elems() * dtype_size(x->dtype);
+    int rc = cuda_fail(cudaMemcpyAsync(out, x->buf.data, bytes, cudaMemcpyDeviceToHost, stream_), "get_local copy");
+    if (rc) return rc;
+    stats_.bytes_d2h += bytes;
+    return synchronize();
+}
+
+int Context::put(int name, int ndims, const int64_t* shape, int dtype, const void* host) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    cudaSetDevice(device_);
+    if (!host) return fail(CN_ERR_INVALID_ARGUMENT, "put: null host buffer");
+    Array* x = nullptr;
+    int rc = create_array(name, ndims, shape, dtype, false, &x);
+    if (rc) return rc;
+    const size_t esz = dtype_size(dtype);
+    const size_t bytes = (size_t)x->local_elems() * esz;
+    const char* src = (const char*)host + (size_t)x->row_begin * x->unit * esz;
+    if (bytes) {
+        if ((rc = cuda_fail(cudaMemcpyAsync(x->buf.data, src, bytes, cudaMemcpyHostToDevice, stream_), "put copy"))) return rc;
+        stats_.bytes_h2d += bytes;
+    }
+    x->halo_valid = false;
+    return CN_OK;
+}
+
+int Context::timer_start() {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    return cuda_fail(cudaEventRecord(ev_start_, stream_), "cudaEventRecord");
+}
+
+int Context::timer_stop(float* ms) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    int rc = cuda_fail(cudaEventRecord(ev_stop_, stream_), "cudaEventRecord");
+    if (rc) return rc;
+    if ((rc = cuda_fail(cudaEventSynchronize(ev_stop_), "cudaEventSynchronize"))) return rc;
+    return cuda_fail(cudaEventElapsedTime(ms, ev_start_, ev_stop_), "cudaEventElapsedTime");
+}
+
+// ---- kernel-ABI level: compile a group, launch it on caller-provided strided views ----------
+
+int Context::compile_group(const char* blob, int64_t size, uint64_t* handle) {
+    DagNode node;
+    int rc = parse_node(blob, size, &node, &err_);
+    if (rc) return rc;
+    GroupIR g;
+    if ((rc = lower_group(node, {}, &g, &err_, true))) return rc;
+    std::string src;
+    if ((rc = generate_source(g, &src, &err_))) return rc;
+    if (initialised_) {
+        cudaSetDevice(device_);
+        CompiledGroup* k = nullptr;
+        if ((rc = get_kernel(g, &k))) return rc;
+    } else {
+        // no device: still prove that the source compiles for sm_100a
+        std::vector<char> cubin;
+        std::string log;
+        if ((rc = nvrtc_compile(src, tile_, &cubin, &log))) return fail(rc, "group kernel failed to compile:\n" + log);
+    }
+    handles_.push_back({src, g});
+    *handle = handles_.size();
+    return CN_OK;
+}
+
+int Context::group_source(uint64_t handle, const char** src) {
+    if (handle == 0 || handle > handles_.size()) return fail(CN_ERR_INVALID_ARGUMENT, "bad group handle");
+    *src = handles_[handle - 1].first.c_str();
+    return CN_OK;
+}
+
+int Context::launch_group(uint64_t handle, int n_in, void* const* in_ptrs, const int64_t* in_off,
+                          const int64_t* in_str, int n_bc, void* const* bc_ptrs, int n_out,
+                          void* const* out_ptrs, const int64_t* out_off, const int64_t* out_str,
+                          const int64_t* ext) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    if (handle == 0 || handle > handles_.size()) return fail(CN_ERR_INVALID_ARGUMENT, "bad group handle");
+    cudaSetDevice(device_);
+    const GroupIR& g = handles_[handle - 1].second;
+    if (g.cls == GroupIR::SCALAR_ONLY || !g.reds.empty() || !g.souts.empty())
+        return fail(CN_ERR_UNSUPPORTED, "raw launch supports array-valued groups without reductions");
+    if (n_in != (int)g.leaves.size() || n_out != (int)g.outs.size() || n_bc != (int)g.bcast_names.size())
+        return fail(CN_ERR_INVALID_ARGUMENT, "argument counts differ from the compiled group");
+    CompiledGroup* k = nullptr;
+    int rc = get_kernel(g, &k);
+    if (rc) return rc;
+    CnGroupArgs a;
+    memset(&a, 0, sizeof(a));
+    for (size_t i = 0; i < g.scalars.size(); ++i) a.sc[i] = g.scalars[i];
+    for (int i = 0; i < n_bc; ++i) a.bc[i] = bc_ptrs[i];
+    const int nd = g.ndims;
+    for (int i = 0; i < n_in; ++i) {
+        a.in[i] = in_ptrs[i];
+        a.in_off[i] = in_off[i];
+        for (int d = 0; d < nd; ++d) a.in_str[i][d] = in_str[i * nd + d];
+    }
+    for (int m = 0; m < n_out; ++m) {
+        a.out[m] = out_ptrs[m];
+        a.out_off[m] = out_off[m];
+        for (int d = 0; d < nd; ++d) a.out_str[m][d] = out_str[m * nd + d];
+    }
+    int64_t total = 1;
+    for (int d = 0; d < 3; ++d) {
+        a.ext[d] = d < nd ? ext[d] : 1;
+        total *= a.ext[d];
+    }
+    if (total <= 0) return CN_OK;
+    int grid = (int)std::min<int64_t>((total + CN_BLOCK - 1) / CN_BLOCK, (int64_t)sm_count_ * 8);
+    return launch(k, a, grid, CN_BLOCK);
+}
+
+}  // namespace cn

@@ -1,0 +1,115 @@
+// NVRTC front end.  libnvrtc is opened with dlopen on first use so that the library loads
+// (and its host-side logic can be tested) on machines without the CUDA toolkit libraries
+// on the loader path.
+#include "jit.hpp"
+
+#include <dlfcn.h>
+
+#include <cstdlib>
+#include <mutex>
+
+namespace cn {
+
+namespace {
+
+typedef struct _nvrtcProgram* nvrtcProgram;
+typedef int nvrtcResult;
+
+struct NvrtcApi {
+    void* handle = nullptr;
+    nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*,
+                                 const char* const*) = nullptr;
+    nvrtcResult (*DestroyProgram)(nvrtcProgram*) = nullptr;
+    nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*) = nullptr;
+    nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*) = nullptr;
+    nvrtcResult (*GetCUBIN)(nvrtcProgram, char*) = nullptr;
+    nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*) = nullptr;
+    nvrtcResult (*GetProgramLog)(nvrtcProgram, char*) = nullptr;
+    const char* (*GetErrorString)(nvrtcResult) = nullptr;
+    std::string error;
+};
+
+NvrtcApi* load_nvrtc() {
+    static NvrtcApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char* env = getenv("CN_NVRTC_LIB");
+        const char* candidates[] = {env,
+                                    "/usr/local/cuda/lib64/libnvrtc.so.12",
+                                    "libnvrtc.so.12",
+                                    "/usr/local/cuda/lib64/libnvrtc.so",
+                                    "libnvrtc.so"};
+        for (const char* c : candidates) {
+            if (!c || !*c) continue;
+            api.handle = dlopen(c, RTLD_NOW | RTLD_LOCAL);
+            if (api.handle) break;
+        }
+        if (!api.handle) {
+            api.error = "libnvrtc not found (set CN_NVRTC_LIB to its path)";
+            return;
+        }
+#define CN_SYM(name)                                                            \
+    api.name = reinterpret_cast<decltype(api.name)>(dlsym(api.handle, "nvrtc" #name)); \
+    if (!api.name) api.error = "libnvrtc lacks nvrtc" #name;
+        CN_SYM(CreateProgram)
+        CN_SYM(DestroyProgram)
+        CN_SYM(CompileProgram)
+        CN_SYM(GetCUBINSize)
+        CN_SYM(GetCUBIN)
+        CN_SYM(GetProgramLogSize)
+        CN_SYM(GetProgramLog)
+        CN_SYM(GetErrorString)
+#undef CN_SYM
+    });
+    return &api;
+}
+
+}  // namespace
+
+int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector<char>* cubin,
+                  std::string* log) {
+    NvrtcApi* api = load_nvrtc();
+    if (!api->handle || !api->error.empty()) {
+        if (log) *log = api->error;
+        return CN_ERR_COMPILE;
+    }
+    const char* headers[] = {kDeviceHeaderText, kExpTableText};
+    const char* names[] = {"cn_device.cuh", "cn_exp_table.inc"};
+    nvrtcProgram prog = nullptr;
+    nvrtcResult rc = api->CreateProgram(&prog, source.c_str(), "cn_group.cu", 2, headers, names);
+    if (rc != 0) {
+        if (log) *log = std::string("nvrtcCreateProgram: ") + api->GetErrorString(rc);
+        return CN_ERR_COMPILE;
+    }
+    std::string d_tx = "-DCN_TX=" + std::to_string(tile.tx);
+    std::string d_r = "-DCN_R=" + std::to_string(tile.r);
+    // --fmad=false: a*b+c stays two roundings, as in the reference's arith.mulf/addf pairs
+    // (src/jit.cpp:411-443); division and sqrt stay IEEE-rounded (the defaults, spelled out).
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false",    "--prec-div=true",
+                          "--prec-sqrt=true",           "--std=c++17",     "-lineinfo",
+                          d_tx.c_str(),                 d_r.c_str()};
+    rc = api->CompileProgram(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);
+    size_t logsz = 0;
+    api->GetProgramLogSize(prog, &logsz);
+    if (log && logsz > 1) {
+        log->resize(logsz);
+        api->GetProgramLog(prog, &(*log)[0]);
+    }
+    if (rc != 0) {
+        if (log) *log = std::string("nvrtcCompileProgram: ") + api->GetErrorString(rc) + "\n" + *log;
+        api->DestroyProgram(&prog);
+        return CN_ERR_COMPILE;
+    }
+    size_t sz = 0;
+    api->GetCUBINSize(prog, &sz);
+    cubin->resize(sz);
+    api->GetCUBIN(prog, cubin->data());
+    api->DestroyProgram(&prog);
+    if (sz == 0) {
+        if (log) *log += "\nNVRTC produced no cubin";
+        return CN_ERR_COMPILE;
+    }
+    return CN_OK;
+}
+
+}  // namespace cn

@@ -1,0 +1,30 @@
+// Run-time compilation of generated group kernels (NVRTC -> cubin for sm_100a) and the
+// function cache keyed by the group's structural key.
+//
+// Counterpart of ArrayDAGGroup::compile_node / module_cache in the reference
+// (src/dag_group_compile.cpp:6-56) and of MLIRJitCompiler::generateNVIDIA / loadNVIDIA
+// (src/jit.cpp:463-540), which emit PTX for sm_70 and load it with the driver API.
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "group_ir.hpp"
+
+namespace cn {
+
+struct TileConfig {
+    int tx = 64;  // threads along the last dimension
+    int r = 4;    // consecutive rows per thread
+};
+
+// Compile CUDA source to a cubin image for sm_100a.  Works without a GPU.
+// `log` receives the NVRTC log (warnings, errors).
+int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector<char>* cubin,
+                  std::string* log);
+
+// Texts of the headers every generated kernel includes (embedded at build time).
+extern const char* const kDeviceHeaderText;
+extern const char* const kExpTableText;
+
+}  // namespace cn

@@ -1,0 +1,35 @@
+// Launchers of the ahead-of-time CUDA kernels (kernels.cu).  Every launcher enqueues on
+// the given stream and returns the CUDA status of the launch; none synchronises.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace cn {
+
+struct StridedView {  // element offset + element stride per iteration dimension
+    int64_t off = 0;
+    int64_t str[3] = {0, 0, 0};
+};
+
+// SET_REGION with a literal right-hand side (src/executor_ast_visitor.cpp:112-197).
+cudaError_t launch_fill_region(void* base, int dtype, const StridedView& v, const int64_t ext[3],
+                               double value, cudaStream_t s);
+// Strided region copy (src/executor_ast_visitor.cpp:199-314): dst[view] = src[view].
+cudaError_t launch_copy_region(void* dst, const StridedView& dv, const void* src,
+                               const StridedView& sv, const int64_t ext[3], int dtype,
+                               cudaStream_t s);
+// Seeded uniform fill: element with global linear index g gets lo + (hi-lo)*u(seed, g).
+cudaError_t launch_randu(void* data, int dtype, int64_t n_local, int64_t global_offset,
+                         uint64_t seed, double lo, double hi, cudaStream_t s);
+// result[0] = sum_i a[i]*b[i]   (b == nullptr: sum_i a[i]); deterministic two-pass finish.
+// `partials` needs dot_grid_size(n) accumulators, `counter` is a zeroed ticket.
+int dot_grid_size(int64_t n, int sm_count);
+cudaError_t launch_dot(const void* a, const void* b, int64_t n, int dtype, void* partials,
+                       unsigned int* counter, void* result, int grid, cudaStream_t s);
+// y[r] = sum_c A[r*lda + c] * x[c] for r in [0, rows): row-block gemv of the local slab
+// (src/backend_internal.hpp:15-41, src/execute_node.cpp:206-229).
+cudaError_t launch_matvec(const void* A, int64_t lda, const void* x, void* y, int64_t rows,
+                          int64_t cols, int dtype, cudaStream_t s);
+
+}  // namespace cn

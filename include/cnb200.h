@@ -1,0 +1,148 @@
+/*
+ * cnb200 -- C ABI of the B200 execution backend for charmnumeric's data-parallel hot path
+ * (fused elementwise / stencil groups, dot and sum reductions, row-partitioned matvec over
+ * slab-partitioned arrays).  Plain pointers and sizes only; every function returns a status
+ * code (0 = ok) and never aborts the process.  One context drives one GPU; with N GPUs there
+ * are N processes, each with one context of rank r in [0, N).
+ *
+ * Each entry point names the reference interface it stands in for (paths are relative to
+ * the reference tree).
+ */
+#ifndef CNB200_H
+#define CNB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cn_context cn_context;
+
+/* status codes */
+enum {
+    CN_STATUS_OK = 0,
+    CN_STATUS_INVALID_ARGUMENT = 1,
+    CN_STATUS_BAD_BLOB = 2,
+    CN_STATUS_UNKNOWN_ARRAY = 3,
+    CN_STATUS_SHAPE_MISMATCH = 4,
+    CN_STATUS_UNSUPPORTED = 5,
+    CN_STATUS_BAD_OPCODE = 6,
+    CN_STATUS_BAD_DTYPE = 7,
+    CN_STATUS_CUDA = 8,
+    CN_STATUS_COMPILE = 9,
+    CN_STATUS_COMM = 10,
+    CN_STATUS_HAZARD = 11,
+    CN_STATUS_OUT_OF_MEMORY = 12,
+    CN_STATUS_LIMIT = 13,
+    CN_STATUS_RANK_FAILED = 14,
+    CN_STATUS_NO_DEVICE = 15
+};
+
+/* opcode numbering: src/opcodes.hpp:3-20 == charmnumeric/charmnumeric.py:139-150;
+ * values >= 11 are additions of this backend. */
+enum {
+    CN_OP_COPY = -5, CN_OP_SET_REGION = -4, CN_OP_GET_REGION = -3, CN_OP_CREATE = -2,
+    CN_OP_NOOP = -1, CN_OP_ADD = 0, CN_OP_SUB = 1, CN_OP_MUL = 2, CN_OP_DIV = 3,
+    CN_OP_MATMUL = 4, CN_OP_TANH = 5, CN_OP_EXP = 6, CN_OP_TILE = 7, CN_OP_REDUCE = 8,
+    CN_OP_MATMATMUL = 9, CN_OP_DIAG = 10,
+    CN_OP_SQRT = 11, CN_OP_ABS = 12, CN_OP_SUM = 13, CN_OP_RANDU = 14
+};
+
+/* dtype codes: charmnumeric/charmnumeric.py:37-40 */
+enum { CN_DTYPE_F32 = 0, CN_DTYPE_F64 = 1, CN_DTYPE_I32 = 2, CN_DTYPE_I64 = 3 };
+
+int cn_version(void);
+const char* cn_status_string(int status);
+
+/* Context life cycle.  Stands in for Main / ArrayDAGGroup construction and the chare
+ * arrays it creates (src/server.cpp:7-20, src/dag_group_runtime.cpp:7-32).  Fails with
+ * CN_STATUS_NO_DEVICE when no sm_100 GPU is visible: there is no CPU path. */
+int cn_context_create(int device, int rank, int nranks, cn_context** out);
+int cn_context_destroy(cn_context* ctx);
+const char* cn_last_error(cn_context* ctx);
+
+/* Multi-GPU wiring.  Stands in for `charmrun +pN` start-up and proxy broadcast
+ * (charmnumeric/interface.py:74-92, src/dag_group_runtime.cpp:18-28).  Rank 0 obtains an
+ * id, the host program hands the 128 bytes to every rank by any means, every rank calls
+ * cn_comm_init with it. */
+int cn_comm_unique_id(char id[128]);
+int cn_comm_init(cn_context* ctx, const char id[128]);
+/* Host-side failure notice: after a rank is marked failed every call that would need a
+ * collective returns CN_STATUS_RANK_FAILED instead of starting it. */
+int cn_mark_rank_failed(cn_context* ctx, int rank);
+
+/* Execute one DAG.  Stands in for the entry method
+ * ArrayDAGGroup::receive_dag(int epoch, int size, char msg[size]) (src/backend.ci:15,
+ * src/dag_group_receive.cpp:191-575).  `msg` is a CNB1 blob.
+ * Work is enqueued on the context's stream; the call does not wait for the GPU. */
+int cn_receive_dag(cn_context* ctx, int epoch, int64_t size, const char* msg);
+
+/* Fetch a whole array as a row-major host buffer on every calling rank.  Stands in for
+ * receive_get_request(int ndims, int epoch, int name, int size, int dtype) + gather +
+ * send_reply (src/backend.ci:16-17, src/dag_group_runtime.cpp:55-118,
+ * src/partition_get.cpp:3-67).  Waits for all enqueued work. */
+int cn_get(cn_context* ctx, int ndims, int epoch, int name, int64_t count, int dtype, void* out);
+/* This rank's slab only (rows [*row_begin, *row_end) of dimension 0); out may be NULL to
+ * query the range.  No counterpart in the reference (its chares are gathered on PE 0). */
+int cn_get_local(cn_context* ctx, int name, int64_t* row_begin, int64_t* row_end,
+                 int64_t capacity, void* out);
+/* Bulk upload of a whole row-major host array; each rank copies its own slab.  No
+ * counterpart in the reference, which assigns host data one SET_REGION per element
+ * (charmnumeric/charmnumeric.py:863-878). */
+int cn_put(cn_context* ctx, int name, int ndims, const int64_t* shape, int dtype,
+           const void* host);
+
+/* DAGExecutor::delete_array(int name) (src/backend.hpp:334, src/executor_core.cpp:184-192). */
+int cn_delete_array(cn_context* ctx, int name);
+int cn_array_info(cn_context* ctx, int name, int* ndims, int64_t shape[3], int* dtype,
+                  int64_t* row_begin, int64_t* row_end);
+int cn_synchronize(cn_context* ctx);
+
+/* Kernel-ABI level.  cn_compile_group stands in for ArrayDAGGroup::compile_node
+ * (src/dag_group_compile.cpp:6-41): it takes one serialized group (the `node` production
+ * of the CNB1 format) and returns a handle to the compiled kernel.  cn_launch_group stands
+ * in for dispatch_kernel (src/dispatch.hpp:137-265): inputs in leaf discovery order, then
+ * size-1 arrays, then outputs, each array argument as (device pointer, element offset,
+ * element stride per dimension) -- the fields of the reference's MemRef descriptor
+ * (src/array_region.hpp:406-415).  in_str / out_str hold ndims entries per argument. */
+int cn_compile_group(cn_context* ctx, const char* node_blob, int64_t size, uint64_t* handle);
+int cn_group_source(cn_context* ctx, uint64_t handle, const char** source);
+int cn_launch_group(cn_context* ctx, uint64_t handle, int n_in, void* const* in_ptrs,
+                    const int64_t* in_off, const int64_t* in_str, int n_bc,
+                    void* const* bc_ptrs, int n_out, void* const* out_ptrs,
+                    const int64_t* out_off, const int64_t* out_str, const int64_t* ext);
+
+/* Host-only checks (no GPU needed): parse a DAG blob; lower + generate + compile one group
+ * for sm_100a and return its CUDA source (truncated to cap-1 bytes) and cubin size. */
+int cn_dag_check(const char* msg, int64_t size, int* n_nodes, int* n_roots, char* err, int errcap);
+int cn_group_compile_check(const char* node_blob, int64_t size, char* source, int64_t cap,
+                           int64_t* cubin_bytes, char* err, int errcap);
+
+/* Device timing with CUDA events on the context's own stream. */
+int cn_timer_start(cn_context* ctx);
+int cn_timer_stop(cn_context* ctx, float* milliseconds);
+
+/* Counters since context creation. */
+typedef struct cn_stats {
+    int64_t kernel_launches;   /* kernels of this library launched */
+    int64_t group_launches;    /* of which generated group kernels */
+    int64_t compiles;          /* run-time compilations (cache misses) */
+    int64_t halo_exchanges;
+    int64_t allreduces;
+    int64_t fused_reductions;  /* REDUCE / SUM nodes folded into a group kernel */
+    int64_t nodes;             /* DAG nodes executed */
+    int64_t bytes_h2d;
+    int64_t bytes_d2h;
+} cn_stats;
+int cn_get_stats(cn_context* ctx, cn_stats* out);
+
+/* Tuning knobs: halo depth (rows per side, default 1; set before creating arrays),
+ * reduction fusion on/off, tile shape of generated kernels (threads along the last
+ * dimension, rows per thread). */
+int cn_set_option(cn_context* ctx, const char* key, int64_t value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CNB200_H */

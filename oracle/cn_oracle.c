@@ -1,0 +1,421 @@
+/*
+ * CPU oracle: a plain-C restatement of the reference's hot path.  TEST INFRASTRUCTURE ONLY:
+ * it is built and called by tests/, by the smoke check and by the CPU-baseline leg of the
+ * benchmark; the product library never links, loads or calls it.
+ *
+ * What it restates (paths relative to the reference tree):
+ *   - elementwise op semantics: one separately rounded IEEE operation per op, operands in
+ *     (lhs, rhs) order, no fused multiply-add (src/jit.cpp:411-459, emitOp :296-385);
+ *   - SET_REGION: the right-hand side is evaluated completely into a result buffer and
+ *     only then copied into the target (src/execute_node.cpp:1581-1584,
+ *     src/executor_ast_visitor.cpp:199-314) -- so an in-place stencil is a true Jacobi step
+ *     (pinned by tests/test_backend_integration.py:68-105);
+ *   - dot: plain sum of products per tile (Eigen a.dot(b), src/backend_internal.hpp:88-93),
+ *     tile results added one after the other (src/executor_reducer.cpp:18-55);
+ *   - matvec: per-tile gemv, partial results accumulated into the result tile by tile
+ *     (src/backend_internal.hpp:15-41, src/execute_node.cpp:572-576);
+ *   - the tiling of the CPU build: tile = power of two >= CT_MIN_TILE_{1,2,3}D
+ *     (262144 / 512 / 64, src/backend.hpp:15-17), doubled until there are at most
+ *     odf * PEs tiles (src/decomposition_solver.hpp:100-122).
+ * Third-party arithmetic the reference delegates to and that is absent from its tree:
+ * Eigen3 (unpinned) for dot/gemv -- restated as the textbook loops above; libm exp/tanh --
+ * replaced by the table-driven routines below, which the GPU kernels restate step for step
+ * (so exp/tanh results are bit-identical by construction) and which are checked against
+ * this machine's libm to <= 2 ulp in the tests.
+ *
+ * Pinning: the reference ships no golden vector files and cannot be built here (Charm++,
+ * MLIR, Eigen and its parent repository are absent).  The oracle is pinned against the
+ * known answers the reference's own tests state (tests/test_backend_integration.py:13-105,
+ * tests/test_jit.cpp:244-326) and the self-checks of examples/cg.py:65-73 and
+ * examples/matvec.py:45-55.  Dot and matvec have no test under the reference's tests/:
+ * for them parity is UNPINNED beyond those example checks.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see oracle/Makefile).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "cn_oracle_exp_table.h"
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+static double from_bits(uint64_t b) {
+    double d;
+    memcpy(&d, &b, 8);
+    return d;
+}
+static uint64_t to_bits(double d) {
+    uint64_t b;
+    memcpy(&b, &d, 8);
+    return b;
+}
+
+/* ---- exp / tanh ---------------------------------------------------------------------- */
+
+static double scale2(double v, int m) {
+    if (m >= -1000 && m <= 1000) return from_bits(to_bits(v) + ((uint64_t)(int64_t)m << 52));
+    int m1 = m / 2, m2 = m - m1;
+    double p1 = from_bits((uint64_t)(m1 + 1023) << 52);
+    double p2 = from_bits((uint64_t)(m2 + 1023) << 52);
+    return (v * p1) * p2;
+}
+
+/* reduction shared by exp and expm1: x = (64 m + j) ln2/64 + r; returns q = e^r - 1 */
+static double reduce_exp(double x, int* j, int* m) {
+    const double shift = 6755399441055744.0; /* 1.5 * 2^52 */
+    double t = fma(x, CNO_INV, shift);
+    int32_t ki = (int32_t)(uint32_t)(to_bits(t) & 0xffffffffu);
+    double kd = t - shift;
+    double r = fma(-kd, CNO_C_HI, x);
+    r = fma(-kd, CNO_C_LO, r);
+    *j = ki & 63;
+    *m = ki >> 6;
+    double p = fma(r, 0x1.1111111111111p-7, 0x1.5555555555555p-5);
+    p = fma(p, r, 0x1.5555555555555p-3);
+    p = fma(p, r, 0.5);
+    return fma(p, r * r, r);
+}
+
+double cno_exp(double x) {
+    if (x != x) return x;
+    if (x > 709.782712893384) return from_bits(0x7ff0000000000000ull);
+    if (x < -745.1332191019412) return 0.0;
+    int j, m;
+    double q = reduce_exp(x, &j, &m);
+    double hi = CNO_T_HI[j], lo = CNO_T_LO[j];
+    double v = hi + fma(hi, q, lo);
+    return scale2(v, m);
+}
+
+static double expm1_small(double y) {
+    /* same reduction as exp, two more polynomial terms (the result is small) */
+    const double shift = 6755399441055744.0;
+    double t = fma(y, CNO_INV, shift);
+    int32_t ki = (int32_t)(uint32_t)(to_bits(t) & 0xffffffffu);
+    double kd = t - shift;
+    double r = fma(-kd, CNO_C_HI, y);
+    r = fma(-kd, CNO_C_LO, r);
+    int j = ki & 63, m = ki >> 6;
+    double p = fma(r, 0x1.a01a01a01a01ap-13, 0x1.6c16c16c16c17p-10);
+    p = fma(p, r, 0x1.1111111111111p-7);
+    p = fma(p, r, 0x1.5555555555555p-5);
+    p = fma(p, r, 0x1.5555555555555p-3);
+    p = fma(p, r, 0.5);
+    double q = fma(p, r * r, r);
+    double sc = (m == 0) ? 1.0 : ((m == 1) ? 2.0 : 4.0);
+    double hi = CNO_T_HI[j] * sc, lo = CNO_T_LO[j] * sc;
+    return (hi - 1.0) + fma(hi, q, lo);
+}
+
+double cno_tanh(double x) {
+    if (x != x) return x;
+    double ax = x < 0 ? -x : x;
+    double r;
+    if (ax >= 22.0) r = 1.0;
+    else if (ax >= 0.5) {
+        double e = cno_exp(2.0 * ax);
+        r = 1.0 - 2.0 / (e + 1.0);
+    } else if (ax >= 0x1p-28) {
+        double em1 = expm1_small(2.0 * ax);
+        r = em1 / (em1 + 2.0);
+    } else r = ax;
+    return x < 0 ? -r : r;
+}
+
+void cno_exp_v(const double* x, double* y, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) y[i] = cno_exp(x[i]);
+}
+void cno_tanh_v(const double* x, double* y, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) y[i] = cno_tanh(x[i]);
+}
+
+/* ---- seeded uniform fill ---------------------------------------------------------------- */
+/* element g: z = splitmix64-finalise(seed + (g+1)*golden); u = (z >> 11) * 2^-53;
+ * value = lo + (hi - lo) * u, multiply and add rounded separately */
+void cno_randu(double* out, int64_t n, uint64_t goff, uint64_t seed, double lo, double hi) {
+    const double span = hi - lo;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        uint64_t z = seed + (goff + (uint64_t)i + 1ull) * 0x9E3779B97F4A7C15ull;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z = z ^ (z >> 31);
+        double u = (double)(z >> 11) * 0x1p-53;
+        double t = span * u;
+        out[i] = lo + t;
+    }
+}
+
+/* ---- tiling rule of the reference ------------------------------------------------------- */
+int64_t cno_tile(int64_t extent, int ndims, int max_tiles) {
+    int64_t min_tile = ndims == 1 ? 262144 : (ndims == 2 ? 512 : 64);
+    int64_t tile = min_tile;
+    for (;;) {
+        int64_t per_dim = (extent + tile - 1) / tile;
+        int64_t count = 1;
+        for (int d = 0; d < ndims; ++d) count *= per_dim;
+        if (count <= max_tiles || tile >= extent) break;
+        tile *= 2;
+    }
+    return tile;
+}
+
+/* ---- dot and matvec ------------------------------------------------------------------------ */
+double cno_dot(const double* a, const double* b, int64_t n, int64_t tile) {
+    if (tile <= 0) tile = n > 0 ? n : 1;
+    int64_t ntiles = (n + tile - 1) / tile;
+    double* part = (double*)malloc(sizeof(double) * (size_t)(ntiles > 0 ? ntiles : 1));
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < ntiles; ++t) {
+        int64_t lo = t * tile, hi = lo + tile < n ? lo + tile : n;
+        double s = 0.0;
+        for (int64_t i = lo; i < hi; ++i) s += a[i] * b[i];
+        part[t] = s;
+    }
+    double total = 0.0;
+    for (int64_t t = 0; t < ntiles; ++t) total += part[t];
+    free(part);
+    return total;
+}
+
+void cno_gemv(const double* A, int64_t lda, const double* x, double* y, int64_t rows, int64_t cols,
+              int64_t tile) {
+    if (tile <= 0) tile = cols > 0 ? cols : 1;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        double acc = 0.0;
+        for (int64_t c0 = 0; c0 < cols; c0 += tile) { /* one partial per column tile */
+            int64_t c1 = c0 + tile < cols ? c0 + tile : cols;
+            double s = 0.0;
+            for (int64_t c = c0; c < c1; ++c) s += A[r * lda + c] * x[c];
+            acc += s;
+        }
+        y[r] = acc;
+    }
+}
+
+/* ---- workloads ------------------------------------------------------------------------------ */
+/* Each iteration: every tile evaluates the fused stencil group into the result buffer,
+ * then (after all tiles are done) the result is copied into the target -- the reference's
+ * result-buffer-then-copy SET_REGION.  Residual sum((new-old)^2) is accumulated per tile and
+ * the tile sums are added in tile order. */
+
+void cno_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+/* 5-point Jacobi on an n0 x n1 array, interior only; association ((up+down)+left)+right, * c */
+void cno_jacobi2d(double* u, double* result, int64_t n0, int64_t n1, double c, int iters,
+                  int res_every, double* res_out, int64_t tile) {
+    if (tile <= 0) tile = 512;
+    int64_t t0 = (n0 + tile - 1) / tile, t1 = (n1 + tile - 1) / tile;
+    double* part = (double*)malloc(sizeof(double) * (size_t)(t0 * t1));
+    int nres = 0;
+    for (int it = 1; it <= iters; ++it) {
+        int want = res_every > 0 && (it % res_every) == 0;
+#pragma omp parallel for schedule(static) collapse(2)
+        for (int64_t ti = 0; ti < t0; ++ti)
+            for (int64_t tj = 0; tj < t1; ++tj) {
+                int64_t i0 = ti * tile, i1 = i0 + tile < n0 ? i0 + tile : n0;
+                int64_t j0 = tj * tile, j1 = j0 + tile < n1 ? j0 + tile : n1;
+                if (i0 < 1) i0 = 1;
+                if (j0 < 1) j0 = 1;
+                if (i1 > n0 - 1) i1 = n0 - 1;
+                if (j1 > n1 - 1) j1 = n1 - 1;
+                double s = 0.0;
+                for (int64_t i = i0; i < i1; ++i)
+                    for (int64_t j = j0; j < j1; ++j) {
+                        double t = u[(i - 1) * n1 + j] + u[(i + 1) * n1 + j];
+                        t = t + u[i * n1 + j - 1];
+                        t = t + u[i * n1 + j + 1];
+                        double v = c * t;
+                        result[i * n1 + j] = v;
+                        if (want) {
+                            double d = v - u[i * n1 + j];
+                            s += d * d;
+                        }
+                    }
+                part[ti * t1 + tj] = s;
+            }
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 1; i < n0 - 1; ++i)
+            memcpy(u + i * n1 + 1, result + i * n1 + 1, sizeof(double) * (size_t)(n1 - 2));
+        if (want) {
+            double total = 0.0;
+            for (int64_t t = 0; t < t0 * t1; ++t) total += part[t];
+            res_out[nres++] = total;
+        }
+    }
+    free(part);
+}
+
+/* 7-point Jacobi on n0 x n1 x n2; association (((((zm+zp)+ym)+yp)+xm)+xp) * c */
+void cno_jacobi3d(double* u, double* result, int64_t n0, int64_t n1, int64_t n2, double c,
+                  int iters, int res_every, double* res_out, int64_t tile) {
+    if (tile <= 0) tile = 64;
+    const int64_t s0 = n1 * n2, s1 = n2;
+    int64_t t0 = (n0 + tile - 1) / tile, t1 = (n1 + tile - 1) / tile, t2 = (n2 + tile - 1) / tile;
+    double* part = (double*)malloc(sizeof(double) * (size_t)(t0 * t1 * t2));
+    int nres = 0;
+    for (int it = 1; it <= iters; ++it) {
+        int want = res_every > 0 && (it % res_every) == 0;
+#pragma omp parallel for schedule(static) collapse(3)
+        for (int64_t ti = 0; ti < t0; ++ti)
+            for (int64_t tj = 0; tj < t1; ++tj)
+                for (int64_t tk = 0; tk < t2; ++tk) {
+                    int64_t i0 = ti * tile, i1 = i0 + tile < n0 ? i0 + tile : n0;
+                    int64_t j0 = tj * tile, j1 = j0 + tile < n1 ? j0 + tile : n1;
+                    int64_t k0 = tk * tile, k1 = k0 + tile < n2 ? k0 + tile : n2;
+                    if (i0 < 1) i0 = 1;
+                    if (j0 < 1) j0 = 1;
+                    if (k0 < 1) k0 = 1;
+                    if (i1 > n0 - 1) i1 = n0 - 1;
+                    if (j1 > n1 - 1) j1 = n1 - 1;
+                    if (k1 > n2 - 1) k1 = n2 - 1;
+                    double s = 0.0;
+                    for (int64_t i = i0; i < i1; ++i)
+                        for (int64_t j = j0; j < j1; ++j)
+                            for (int64_t k = k0; k < k1; ++k) {
+                                int64_t p = i * s0 + j * s1 + k;
+                                double t = u[p - s0] + u[p + s0];
+                                t = t + u[p - s1];
+                                t = t + u[p + s1];
+                                t = t + u[p - 1];
+                                t = t + u[p + 1];
+                                double v = c * t;
+                                result[p] = v;
+                                if (want) {
+                                    double d = v - u[p];
+                                    s += d * d;
+                                }
+                            }
+                    part[(ti * t1 + tj) * t2 + tk] = s;
+                }
+#pragma omp parallel for schedule(static) collapse(2)
+        for (int64_t i = 1; i < n0 - 1; ++i)
+            for (int64_t j = 1; j < n1 - 1; ++j)
+                memcpy(u + i * s0 + j * s1 + 1, result + i * s0 + j * s1 + 1,
+                       sizeof(double) * (size_t)(n2 - 2));
+        if (want) {
+            double total = 0.0;
+            for (int64_t t = 0; t < t0 * t1 * t2; ++t) total += part[t];
+            res_out[nres++] = total;
+        }
+    }
+    free(part);
+}
+
+/* s = sum(exp(-a*a)*b + sqrt(abs(a)) - 0.5*b*b + a/(1+abs(b))), one fused group, evaluated
+ * in the frontend's operator order:
+ *   t1=a*a; t2=t1*-1; t3=exp(t2); t4=t3*b; t5=abs(a); t6=sqrt(t5); t7=t4+t6; t8=0.5*b;
+ *   t9=t8*b; t10=t7-t9; t11=abs(b); t12=1+t11; t13=a/t12; t14=t10+t13 */
+double cno_chain_value(double a, double b) {
+    double t1 = a * a;
+    double t2 = t1 * -1.0;
+    double t3 = cno_exp(t2);
+    double t4 = t3 * b;
+    double t5 = fabs(a);
+    double t6 = sqrt(t5);
+    double t7 = t4 + t6;
+    double t8 = 0.5 * b;
+    double t9 = t8 * b;
+    double t10 = t7 - t9;
+    double t11 = fabs(b);
+    double t12 = 1.0 + t11;
+    double t13 = a / t12;
+    return t10 + t13;
+}
+
+void cno_chain_v(const double* a, const double* b, double* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = cno_chain_value(a[i], b[i]);
+}
+
+double cno_chain_sum(const double* a, const double* b, int64_t n, int64_t tile) {
+    if (tile <= 0) tile = 262144;
+    int64_t ntiles = (n + tile - 1) / tile;
+    double* part = (double*)malloc(sizeof(double) * (size_t)(ntiles > 0 ? ntiles : 1));
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < ntiles; ++t) {
+        int64_t lo = t * tile, hi = lo + tile < n ? lo + tile : n;
+        double s = 0.0;
+        for (int64_t i = lo; i < hi; ++i) s += cno_chain_value(a[i], b[i]);
+        part[t] = s;
+    }
+    double total = 0.0;
+    for (int64_t t = 0; t < ntiles; ++t) total += part[t];
+    free(part);
+    return total;
+}
+
+/* Matrix-free CG for the 5-point Laplacian on an (m x m) array whose outer ring is the
+ * Dirichlet-zero boundary (unknowns: the (m-2)^2 interior).  Operation order of
+ * examples/cg.py:26-52, one pass over memory per DAG node as the reference executes it:
+ *   Ap = (((4*p - up) - down) - left) - right ; pAp = p.Ap ; alpha = rtr/pAp ;
+ *   x = x + alpha*p ; r = r - alpha*Ap ; rtr' = r.r ; beta = rtr'/rtr ; p = r + beta*p.
+ * b, x, r, p, Ap are m*m arrays; rtr_hist receives rtr' of every iteration. */
+void cno_cg_poisson(const double* b, double* x, double* r, double* p, double* Ap, int64_t m,
+                    int iters, double* rtr_hist, int64_t tile) {
+    const int64_t n = m * m;
+    memset(x, 0, sizeof(double) * (size_t)n);
+    memcpy(r, b, sizeof(double) * (size_t)n);
+    memcpy(p, b, sizeof(double) * (size_t)n);
+    memset(Ap, 0, sizeof(double) * (size_t)n);
+    double rtr = cno_dot(r, r, n, tile);
+    for (int it = 0; it < iters; ++it) {
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 1; i < m - 1; ++i)
+            for (int64_t j = 1; j < m - 1; ++j) {
+                int64_t q = i * m + j;
+                double t = 4.0 * p[q];
+                t = t - p[q - m];
+                t = t - p[q + m];
+                t = t - p[q - 1];
+                t = t - p[q + 1];
+                Ap[q] = t;
+            }
+        double pAp = cno_dot(p, Ap, n, tile);
+        double alpha = rtr / pAp;
+#pragma omp parallel for schedule(static)
+        for (int64_t q = 0; q < n; ++q) {
+            double t = alpha * p[q];
+            x[q] = x[q] + t;
+        }
+#pragma omp parallel for schedule(static)
+        for (int64_t q = 0; q < n; ++q) {
+            double t = alpha * Ap[q];
+            r[q] = r[q] - t;
+        }
+        double rtr_new = cno_dot(r, r, n, tile);
+        double beta = rtr_new / rtr;
+#pragma omp parallel for schedule(static)
+        for (int64_t q = 0; q < n; ++q) {
+            double t = beta * p[q];
+            p[q] = r[q] + t;
+        }
+        rtr = rtr_new;
+        if (rtr_hist) rtr_hist[it] = rtr_new;
+    }
+}
+
+/* Power iteration (examples/reduction.py:5-6 with the sqrt addition):
+ *   y = A x ; s = y.y ; x = y / sqrt(s) */
+void cno_power_iteration(const double* A, double* x, double* y, int64_t n, int steps,
+                         double* norm_hist, int64_t tile) {
+    for (int it = 0; it < steps; ++it) {
+        cno_gemv(A, n, x, y, n, n, tile);
+        double s = cno_dot(y, y, n, 262144);
+        double nrm = sqrt(s);
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) x[i] = y[i] / nrm;
+        if (norm_hist) norm_hist[it] = s;
+    }
+}
