@@ -127,6 +127,21 @@ class Context:
         self._check(self._lib.cn_timer_stop(self._h, C.byref(ms)))
         return float(ms.value)
 
+    def profile(self, on=True):
+        self.set_option("profile", 1 if on else 0)
+
+    def profile_report(self):
+        """Kernels timed since profiling was switched on: list of dicts with label, launches,
+        ms (total device time) and bytes (algorithmic bytes moved)."""
+        buf = C.create_string_buffer(1 << 16)
+        self._check(self._lib.cn_profile_report(self._h, buf, len(buf)))
+        rows = []
+        for line in buf.value.decode().splitlines():
+            label, launches, ms, nbytes = line.split("\t")
+            rows.append({"label": label, "launches": int(launches), "ms": float(ms),
+                         "bytes": float(nbytes)})
+        return rows
+
     def stats(self):
         s = _lib.Stats()
         self._check(self._lib.cn_get_stats(self._h, C.byref(s)))

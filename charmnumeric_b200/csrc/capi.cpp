@@ -191,6 +191,11 @@ int cn_timer_stop(cn_context* ctx, float* milliseconds) {
     return ctx->impl.timer_stop(milliseconds);
 }
 
+int cn_profile_report(cn_context* ctx, char* buf, int64_t cap) {
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.profile_report(buf, cap);
+}
+
 int cn_get_stats(cn_context* ctx, cn_stats* out) {
     if (!ctx || !out) return cn::CN_ERR_INVALID_ARGUMENT;
     const cn::Stats& s = ctx->impl.stats();
@@ -212,6 +217,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
     if (k == "halo") {
         if (value < 0 || value > 8) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_halo((int)value);
+    } else if (k == "profile") {
+        ctx->impl.set_profile(value != 0);
     } else if (k == "fuse_reductions") {
         ctx->impl.set_fuse_reductions(value != 0);
     } else if (k == "tile_tx") {

@@ -94,7 +94,7 @@ struct Gen {
         o << "#include \"cn_device.cuh\"\n";
         o << "typedef " << type_name(g.dtype) << " T;\n";
         o << "typedef " << (is_float() ? "double" : "long long") << " ACC;\n";
-        if (g.vec == 2) o << "typedef double2 T2;\n";
+        if (g.vec == 2) o << "typedef " << (g.dtype == DT_I64 ? "longlong2" : "double2") << " T2;\n";
         o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK) cn_group("
              "const __grid_constant__ CnGroupArgs a) {\n";
         for (size_t i = 0; i < g.scalars.size(); ++i)

@@ -53,6 +53,7 @@ struct CompiledGroup {
     CUmodule module = nullptr;
     CUfunction func = nullptr;
     int blocks_per_sm = 1;  // resident 256-thread blocks per SM, from the occupancy query
+    std::string label;      // short description used by the profile report
     std::string source;
     std::string log;
 };
@@ -100,6 +101,8 @@ public:
                      const int64_t* ext);
     int timer_start();
     int timer_stop(float* ms);
+    void set_profile(bool on) { profile_ = on; }
+    int profile_report(char* buf, int64_t cap);
     int mark_rank_failed(int r);
     int array_info(int name, int* ndims, int64_t* shape, int* dtype, int64_t* row_begin,
                    int64_t* row_end);
@@ -139,7 +142,9 @@ private:
     int bind_scalars(const GroupIR& g, CnGroupArgs* a, std::vector<std::pair<Array*, Buffer>>* swaps);
     int bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::vector<Array*>* results);
     int finish_reductions(const std::vector<Array*>& results);
-    int launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block);
+    int launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes);
+    void prof_start(const std::string& label, double bytes);
+    void prof_stop();
     int get_kernel(const GroupIR& g, CompiledGroup** out);
     int execute_reduce(const AstNode& root);
     int execute_matmul(const AstNode& root);
@@ -171,6 +176,16 @@ private:
     int max_grid_ = 0;
     void* scratch_ = nullptr;  // matvec x gather / get staging
     size_t scratch_bytes_ = 0;
+
+    // per-kernel CUDA-event timing (off by default; see cn_profile_report)
+    struct ProfEntry {
+        long long launches = 0;
+        double bytes = 0;
+        std::vector<std::pair<cudaEvent_t, cudaEvent_t>> events;
+    };
+    bool profile_ = false;
+    std::map<std::string, ProfEntry> prof_;
+    ProfEntry* prof_open_ = nullptr;
 
     std::string err_;
     Stats stats_;

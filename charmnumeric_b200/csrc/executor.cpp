@@ -39,6 +39,15 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     stats_.compiles++;
     if ((rc = driver_fail(drv_.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData"))) return rc;
     if ((rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, "cn_group"), "cuModuleGetFunction"))) return rc;
+    {
+        const char* cls = g.cls == GroupIR::SHIFTED ? (g.flat ? "flat" : "shifted")
+                          : (g.cls == GroupIR::STRIDED ? "strided" : "scalar");
+        char lbl[160];
+        snprintf(lbl, sizeof(lbl), "group%zu[%s %dd vec%d in%zu out%zu red%zu%s]", kernels_.size(), cls,
+                 g.ndims, g.vec, g.input_arrays().size(), g.outs.size(), g.reds.size(),
+                 g.copy_through ? " copy-through" : "");
+        k.label = lbl;
+    }
     int occ = 0;
     if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, CN_BLOCK, 0) == CUDA_SUCCESS && occ > 0)
         k.blocks_per_sm = occ;
@@ -47,11 +56,60 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     return CN_OK;
 }
 
-int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block) {
+void Context::prof_start(const std::string& label, double bytes) {
+    if (!profile_) return;
+    ProfEntry& e = prof_[label];
+    e.launches++;
+    e.bytes += bytes;
+    cudaEvent_t a = nullptr, b = nullptr;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    cudaEventRecord(a, stream_);
+    e.events.push_back({a, b});
+    prof_open_ = &e;
+}
+
+void Context::prof_stop() {
+    if (!profile_ || !prof_open_) return;
+    cudaEventRecord(prof_open_->events.back().second, stream_);
+    prof_open_ = nullptr;
+}
+
+// One line per kernel: label <tab> launches <tab> total_ms <tab> algorithmic_bytes
+int Context::profile_report(char* buf, int64_t cap) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    int rc = synchronize();
+    if (rc) return rc;
+    std::string out;
+    for (auto& kv : prof_) {
+        double ms = 0;
+        for (auto& ev : kv.second.events) {
+            float t = 0;
+            if (cudaEventElapsedTime(&t, ev.first, ev.second) == cudaSuccess) ms += t;
+            cudaEventDestroy(ev.first);
+            cudaEventDestroy(ev.second);
+        }
+        char line[512];
+        snprintf(line, sizeof(line), "%s\t%lld\t%.6f\t%.0f\n", kv.first.c_str(), kv.second.launches, ms,
+                 kv.second.bytes);
+        out += line;
+    }
+    prof_.clear();
+    if (buf && cap > 0) {
+        size_t n = std::min<size_t>(out.size(), (size_t)cap - 1);
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return CN_OK;
+}
+
+int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes) {
     void* params[] = {(void*)&a};
+    prof_start(k->label, bytes);
     int rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, 0,
                                            (CUstream)stream_, params, nullptr),
                          "cuLaunchKernel");
+    prof_stop();
     if (rc) return rc;
     stats_.kernel_launches++;
     stats_.group_launches++;
@@ -147,7 +205,7 @@ int Context::run_scalar_only(const GroupIR& g, CompiledGroup* k) {
     std::vector<std::pair<Array*, Buffer>> swaps;
     int rc = bind_scalars(g, &a, &swaps);
     if (rc) return rc;
-    return launch(k, a, 1, 32);
+    return launch(k, a, 1, 32, 0.0);
 }
 
 int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
@@ -285,7 +343,13 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     }
 
     if (ntiles > 0 || !g.reds.empty() || !g.souts.empty()) {
-        if ((rc = launch(k, a, grid, CN_BLOCK))) return rc;
+        // algorithmic bytes: every distinct array read once, every output written once
+        double vol = 1;
+        if (g.flat) vol = (double)ref->local_elems();
+        else for (int d = 0; d < nd; ++d) vol *= (double)std::max<int64_t>(0, hi[d] - lo[d]);
+        if (empty) vol = 0;
+        double bytes = vol * (double)(in_names.size() + g.outs.size()) * dtype_size(g.dtype);
+        if ((rc = launch(k, a, grid, CN_BLOCK, bytes))) return rc;
     }
     for (size_t m = 0; m < outs.size(); ++m) {
         Array* x = outs[m];
@@ -412,7 +476,9 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
         a.red[q] = results[q]->buf.data;
     }
     if (total > 0 || !g.reds.empty() || !g.souts.empty())
-        if ((rc = launch(k, a, grid, CN_BLOCK))) return rc;
+        if ((rc = launch(k, a, grid, CN_BLOCK,
+                         (double)total * (double)(g.leaves.size() + g.outs.size()) * dtype_size(g.dtype))))
+            return rc;
     for (auto& p : copy_back) {
         Array* x = find(p.target->name);
         StridedView dv, sv;
@@ -490,7 +556,10 @@ int Context::execute_reduce(const AstNode& r) {
     if ((rc = create_array(r.result_name, 1, one, dtype, false, &res))) return rc;
     int grid = dot_grid_size(n, sm_count_);
     if (grid > max_grid_) grid = max_grid_;
-    if ((rc = cuda_fail(launch_dot(px, py, n, dtype, partials_, counter_, res->buf.data, grid, stream_), "dot"))) return rc;
+    prof_start(py ? "dot" : "sum", (double)n * (py ? 2 : 1) * dtype_size(dtype));
+    rc = cuda_fail(launch_dot(px, py, n, dtype, partials_, counter_, res->buf.data, grid, stream_), "dot");
+    prof_stop();
+    if (rc) return rc;
     stats_.kernel_launches++;
     std::vector<Array*> results{res};
     return finish_reductions(results);
@@ -524,7 +593,10 @@ int Context::execute_matmul(const AstNode& r) {
     if (nranks_ == 1) {
         const char* pa = A->buf.data + (ra.start[0] * A->shape[1] + ra.start[1]) * esz;
         const char* px = x->buf.data + rx.start[0] * esz;
-        if ((rc = cuda_fail(launch_matvec(pa, A->shape[1], px, y->buf.data, rows, cols, dtype, stream_), "matvec"))) return rc;
+        prof_start("matvec", ((double)rows * cols + rows + cols) * esz);
+        rc = cuda_fail(launch_matvec(pa, A->shape[1], px, y->buf.data, rows, cols, dtype, stream_), "matvec");
+        prof_stop();
+        if (rc) return rc;
         stats_.kernel_launches++;
         y->halo_valid = false;
         return CN_OK;
@@ -543,7 +615,10 @@ int Context::execute_matmul(const AstNode& r) {
         if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * esz, e - b, dtype, p, stream_, &err_))) return rc;
     }
     if ((rc = comm_group_end(&err_))) return rc;
-    if ((rc = cuda_fail(launch_matvec(A->buf.data, A->shape[1], scratch_, y->buf.data, A->local_rows(), cols, dtype, stream_), "matvec"))) return rc;
+    prof_start("matvec", ((double)A->local_rows() * cols + A->local_rows() + cols) * esz);
+    rc = cuda_fail(launch_matvec(A->buf.data, A->shape[1], scratch_, y->buf.data, A->local_rows(), cols, dtype, stream_), "matvec");
+    prof_stop();
+    if (rc) return rc;
     stats_.kernel_launches++;
     y->halo_valid = false;
     return CN_OK;
@@ -725,7 +800,7 @@ int Context::launch_group(uint64_t handle, int n_in, void* const* in_ptrs, const
     }
     if (total <= 0) return CN_OK;
     int grid = (int)std::min<int64_t>((total + CN_BLOCK - 1) / CN_BLOCK, (int64_t)sm_count_ * 8);
-    return launch(k, a, grid, CN_BLOCK);
+    return launch(k, a, grid, CN_BLOCK, (double)total * (n_in + n_out) * dtype_size(g.dtype));
 }
 
 }  // namespace cn

@@ -347,12 +347,34 @@ struct Lowering {
                 int nd[2] = {0, 0};
                 int64_t sh[2][kMaxDims] = {{0, 0, 0}, {0, 0, 0}};
                 ValRef v[2];
+                int n_scalar = 0;
                 for (int k = 0; k < need; ++k) {
                     bool sv = false;
                     int rc = resolve(r->operands[k], -1, redidx, k, &v[k], &sv, &nd[k], sh[k]);
                     if (rc) return rc;
-                    if (sv) return fail(CN_ERR_UNSUPPORTED, "reduction of a scalar value");
+                    if (sv) ++n_scalar;
                 }
+                if (n_scalar == need) {
+                    // sum / dot of size-1 values: a plain scalar root
+                    if ((int)g.souts.size() >= CN_MAX_SOUT)
+                        return fail(CN_ERR_LIMIT, "too many scalar outputs in one group");
+                    RootIR ri;
+                    ri.opcode = need == 2 ? OP_MUL : OP_COPY;
+                    ri.a = v[0];
+                    ri.b = v[1];
+                    ri.result_name = r->result_name;
+                    ri.domain = DOM_SCALAR;
+                    int ridx = (int)g.roots.size();
+                    g.roots.push_back(ri);
+                    root_by_name[r->result_name] = ridx;
+                    ScalarOutIR so;
+                    so.name = r->result_name;
+                    so.value.kind = ValRef::ROOT;
+                    so.value.idx = ridx;
+                    g.souts.push_back(so);
+                    continue;
+                }
+                if (n_scalar) return fail(CN_ERR_UNSUPPORTED, "dot of a scalar with an array");
                 if (need == 2 && (nd[0] != nd[1] || !same_shape(nd[0], sh[0], sh[1])))
                     return fail(CN_ERR_SHAPE_MISMATCH, "dot operands have different shapes");
                 if (!g.ndims) g.ndims = nd[0];

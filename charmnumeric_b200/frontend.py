@@ -722,6 +722,7 @@ class _Group:
         self.uniform = True        # every array touched has array_shape and unit-step views
         self.written = {}          # info.name -> destination Region
         self.produced = set()      # names of elementwise results inside the group
+        self.filled = set()        # arrays assigned from a literal inside the group
 
 
 def _op_views(op):
@@ -748,6 +749,8 @@ def _can_join(g, op):
         return True
     # hazards first
     for info, region in _op_views(op):
+        if info.name in g.filled:
+            return False
         if info.name in g.written and not _is_size1(info):
             dest = g.written[info.name]
             reg = region if region is not None else _full_region(info.shape)
@@ -794,6 +797,8 @@ def _join(g, op):
                 g.uniform = False
     if op.kind == "set":
         g.written[op.result.name] = op.region
+        if not isinstance(op.operands[0], tuple):
+            g.filled.add(op.result.name)
     elif op.kind == "ew":
         g.produced.add(op.result.name)
 
@@ -921,7 +926,9 @@ def execute(interface, mirror=None):
     that receives exactly what the backend receives, in the same order; the tests pass the
     CPU oracle here so both sides execute one and the same DAG."""
     ops, _state.pending = _state.pending, []
-    ctx = interface.context if interface is not None else None
+    ctx = getattr(interface, "context", None)
+    if mirror is None:
+        mirror = getattr(interface, "mirror", None)
     items = build_nodes(ops)
     nodes = []
 

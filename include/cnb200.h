@@ -123,6 +123,13 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
 int cn_timer_start(cn_context* ctx);
 int cn_timer_stop(cn_context* ctx, float* milliseconds);
 
+/* Per-kernel timing.  After cn_set_option(ctx, "profile", 1) every kernel launch of the
+ * library is bracketed by CUDA events on the context's stream; cn_profile_report waits for
+ * the stream, writes one line per kernel -- label <tab> launches <tab> total milliseconds
+ * <tab> algorithmic bytes moved -- and clears the records.  No counterpart in the reference
+ * (it has no timers at all). */
+int cn_profile_report(cn_context* ctx, char* buf, int64_t cap);
+
 /* Counters since context creation. */
 typedef struct cn_stats {
     int64_t kernel_launches;   /* kernels of this library launched */
@@ -137,9 +144,9 @@ typedef struct cn_stats {
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
-/* Tuning knobs: halo depth (rows per side, default 1; set before creating arrays),
- * reduction fusion on/off, tile shape of generated kernels (threads along the last
- * dimension, rows per thread). */
+/* Options: "halo" depth (rows per side, default 1; set before creating arrays),
+ * "fuse_reductions" 0/1, "tile_tx" / "tile_rows" (shape of generated kernels: threads along
+ * the last dimension, rows per thread), "profile" 0/1. */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus

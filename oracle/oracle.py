@@ -245,8 +245,10 @@ class Oracle:
                     s = np.sum(np.asarray(a, np.int64))
                 self.arrays[r.result_name] = np.array([s], dtype=dtype)
             elif op == OP_MATMUL:
-                A = self._leaf_value(r.operands[0][0], r.operands[0][1], dtype)
-                x = self._leaf_value(r.operands[1][0], r.operands[1][1], dtype)
+                A = self.arrays[r.operands[0][0].result_name]
+                A = A[_slices(r.operands[0][1], A.shape)]
+                x = self.arrays[r.operands[1][0].result_name]
+                x = x[_slices(r.operands[1][1], x.shape)]
                 if dtype == np.float64:
                     y = gemv(A, x, ref_tile(A.shape[1], 2))
                 else:
