@@ -57,6 +57,7 @@ SIGNATURES = {
                                C.c_char_p, C.c_int]),
     "cn_group_compile_check": (C.c_int, [C.c_char_p, C.c_int64, C.c_char_p, C.c_int64, _I64P,
                                          C.c_char_p, C.c_int]),
+    "cn_partition": (C.c_int, [C.c_int64, C.c_int, C.c_int, _I64P, _I64P]),
     "cn_timer_start": (C.c_int, [_P]),
     "cn_timer_stop": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "cn_profile_report": (C.c_int, [_P, C.c_char_p, C.c_int64]),

@@ -181,6 +181,13 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
     return cn::CN_OK;
 }
 
+int cn_partition(int64_t n0, int nranks, int rank, int64_t* begin, int64_t* end) {
+    if (n0 < 0 || nranks < 1 || rank < 0 || rank >= nranks || !begin || !end)
+        return cn::CN_ERR_INVALID_ARGUMENT;
+    cn::slab_partition(n0, nranks, rank, begin, end);
+    return cn::CN_OK;
+}
+
 int cn_timer_start(cn_context* ctx) {
     if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
     return ctx->impl.timer_start();
@@ -217,6 +224,14 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
     if (k == "halo") {
         if (value < 0 || value > 8) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_halo((int)value);
+    } else if (k == "staged") {
+        cn::set_staged_enabled(value != 0);
+    } else if (k == "staged_tile_tx") {
+        if (value < 8 || value > 64 || 256 % value) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_staged_tile((int)value, -1);
+    } else if (k == "staged_tile_rows") {
+        if (value < 1 || value > 16) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_staged_tile(-1, (int)value);
     } else if (k == "profile") {
         ctx->impl.set_profile(value != 0);
     } else if (k == "fuse_reductions") {

@@ -17,7 +17,12 @@
 
 // Launch arguments of one fused group kernel.  The same layout is used by the host
 // (it fills the block) and by the generated source (it reads it), so only plain types.
-struct CnGroupArgs {
+struct
+#if defined(__CUDACC__) || defined(__GNUC__)
+    __attribute__((aligned(64)))
+#endif
+    CnGroupArgs {
+    unsigned char tmap[128];     // staged kernels: TMA descriptor of the stencil array (64-byte aligned)
     const void* in[CN_MAX_IN];   // array leaves: address of local element (0,0,0)
     void* out[CN_MAX_OUT];       // outputs: address of local element (0,0,0) of the buffer written
     const void* old[CN_MAX_OUT]; // previous contents of each output array
@@ -37,6 +42,9 @@ struct CnGroupArgs {
     double* partials;            // [CN_MAX_RED][gridDim.x] per-block partial sums
     unsigned int* counter;       // ticket for the last-block finish (left at 0 on exit)
     void* red[CN_MAX_RED];       // reduction results (size-1 arrays)
+    long long nzc, zchunk;       // staged 3-D kernels: number and length of the z chunks marched
+    long long tm_off[3];         // staged kernels: local coordinate -> descriptor coordinate offset
+    unsigned int* error;         // device error word (set when a bounded wait runs out)
 };
 
 #ifdef __CUDACC__
@@ -169,6 +177,65 @@ __device__ __forceinline__ A cn_sum_partials(const A* partials, A* smem) {
     for (unsigned int i = threadIdx.x; i < gridDim.x; i += blockDim.x)
         v += ((const volatile A*)partials)[i];
     return cn_block_sum(v, smem);  // valid in thread 0
+}
+
+// ---- TMA / mbarrier helpers (sm_100a) -----------------------------------------------------
+// Tiles of the stencil array are fetched by the TMA unit into a ring of shared-memory
+// slots; one mbarrier per slot counts the bytes that arrive.  Every wait is bounded: when
+// the bound runs out the kernel records it in the error word and leaves.
+#define CN_WAIT_LIMIT 20000000u
+
+__device__ __forceinline__ unsigned int cn_smem_addr(const void* p) {
+    return (unsigned int)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void cn_mbar_init(unsigned long long* bar, unsigned int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(cn_smem_addr(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void cn_mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void cn_mbar_expect_tx(unsigned long long* bar, unsigned int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cn_smem_addr(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+// true when the phase with the given parity has completed; false when the bound ran out
+__device__ __forceinline__ bool cn_mbar_wait(unsigned long long* bar, unsigned int parity) {
+    const unsigned int addr = cn_smem_addr(bar);
+    for (unsigned int i = 0; i < CN_WAIT_LIMIT; ++i) {
+        unsigned int done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void cn_tma_load_2d(void* dst, const void* tmap, int x, int y,
+                                               unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(cn_smem_addr(dst)), "l"(tmap), "r"(x), "r"(y), "r"(cn_smem_addr(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void cn_tma_load_3d(void* dst, const void* tmap, int x, int y, int z,
+                                               unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(cn_smem_addr(dst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(cn_smem_addr(bar))
+        : "memory");
 }
 
 #endif  // __CUDACC__

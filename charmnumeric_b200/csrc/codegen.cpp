@@ -70,6 +70,7 @@ struct Gen {
         return "(T)0";
     }
 
+    bool staged_mode = false;  // stencil array comes from the shared-memory ring
     // slot of each distinct input array, in order of first use (SHIFTED class)
     std::vector<int> in_names;
     int in_slot(int name) {
@@ -95,7 +96,7 @@ struct Gen {
         o << "typedef " << type_name(g.dtype) << " T;\n";
         o << "typedef " << (is_float() ? "double" : "long long") << " ACC;\n";
         if (g.vec == 2) o << "typedef " << (g.dtype == DT_I64 ? "longlong2" : "double2") << " T2;\n";
-        o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK) cn_group("
+        o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK) " << g.entry_name() << "("
              "const __grid_constant__ CnGroupArgs a) {\n";
         for (size_t i = 0; i < g.scalars.size(); ++i)
             o << "  const T c" << i << " = (T)a.sc[" << i << "];\n";
@@ -207,20 +208,31 @@ struct Gen {
             std::ostringstream decl;
             for (int64_t c : row.cols) decl << ind << "T " << colname((int)r, c) << " = (T)0;\n";
             o << decl.str();
-            o << ind << "if " << guard_any(row.domain) << " {\n";
+            // where the row lives: global memory (guarded) or the shared-memory ring (always
+            // there: the TMA unit zero-fills whatever lies outside the array)
+            const bool smem = staged_mode && row.name == g.stage_array;
+            std::ostringstream base;
+            if (smem) {
+                const int64_t dz = N == 3 ? row.d0 : 0, dy = N == 3 ? row.d1 : row.d0;
+                base << "sp" << (dz + g.hz) << " + sq + (" << dy << ") * CN_SW + 2";
+                o << ind << "{\n";
+            } else {
+                base << "in" << slot << " + p" << row.off;
+                o << ind << "if " << guard_any(row.domain) << " {\n";
+            }
             std::set<int64_t> done;
             for (int64_t c : row.cols) {
                 if (done.count(c)) continue;
                 bool even = ((c % 2) + 2) % 2 == 0;
                 if (V == 2 && even && row.cols.count(c + 1)) {
-                    o << ind << "  { const T2 q = *(const T2*)(in" << slot << " + p" << row.off
-                      << " + (" << c << "LL)); " << colname((int)r, c) << " = q.x; "
-                      << colname((int)r, c + 1) << " = q.y; }\n";
+                    o << ind << "  { const T2 q = *(const T2*)(" << base.str() << " + (" << c
+                      << "LL)); " << colname((int)r, c) << " = q.x; " << colname((int)r, c + 1)
+                      << " = q.y; }\n";
                     done.insert(c);
                     done.insert(c + 1);
                 } else {
-                    o << ind << "  " << colname((int)r, c) << " = in" << slot << "[p" << row.off
-                      << " + (" << c << "LL)];\n";
+                    o << ind << "  " << colname((int)r, c) << " = *(" << base.str() << " + (" << c
+                      << "LL));\n";
                     done.insert(c);
                 }
             }
@@ -237,12 +249,32 @@ struct Gen {
         for (size_t m = 0; m < g.outs.size(); ++m) {
             if (!g.outs[m].needs_old) continue;
             for (int e = 0; e < V; ++e) o << ind << "T old" << m << "_" << e << " = (T)0;\n";
-            o << ind << "if " << guard_any(DOM_BOX) << " {\n";
+            // only elements of the sweep that lie outside the assigned region keep their
+            // old value; inside it nothing of the old contents is needed
+            if (g.two_domains && g.outs[m].domain == DOM_REGION) {
+                if (V == 2) o << ind << "if ((bx0 & !act0) | (bx1 & !act1)) {\n";
+                else o << ind << "if (bx0 & !act0) {\n";
+            } else {
+                o << ind << "if " << guard_any(DOM_BOX) << " {\n";
+            }
+            // the old contents live in the buffer the group also reads as an input: go through
+            // that pointer so that the load coincides with the stencil's centre-row load
+            std::ostringstream ptr;
+            ptr << "old" << m << " + p";
+            for (size_t s = 0; s < in_names.size(); ++s)
+                if (in_names[s] == g.outs[m].name) {
+                    ptr.str("");
+                    ptr << "in" << s << " + p";
+                }
+            if (staged_mode && g.outs[m].name == g.stage_array) {
+                ptr.str("");
+                ptr << "sp" << g.hz << " + sq + (0) * CN_SW + 2";
+            }
             if (V == 2) {
-                o << ind << "  const T2 q = *(const T2*)(old" << m << " + p);\n";
+                o << ind << "  const T2 q = *(const T2*)(" << ptr.str() << " + (0LL));\n";
                 o << ind << "  old" << m << "_0 = q.x; old" << m << "_1 = q.y;\n";
             } else {
-                o << ind << "  old" << m << "_0 = old" << m << "[p];\n";
+                o << ind << "  old" << m << "_0 = *(" << ptr.str() << " + (0LL));\n";
             }
             o << ind << "}\n";
         }
@@ -330,13 +362,57 @@ struct Gen {
             o << "  const long long rxlo = a.rlo[" << L << "], rxhi = a.rhi[" << L << "];\n";
         o << "  const long long xbase = " << (V == 2 ? "xlo & ~1LL" : "xlo") << ";\n";
         o << "  const unsigned int ntiles = (unsigned int)a.ntiles;\n";
-        if (N == 1) {
-            o << "  for (unsigned int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+        // Tiles that lie completely inside the region take a path without any per-element
+        // guard: every load is unconditional, so the compiler can issue the loads of all
+        // CN_R rows up front and reuse rows shared by consecutive stencil rows.
+        auto emit_guards = [&](bool fast) {
+            if (fast) {
+                for (int e = 0; e < V; ++e) o << "      const bool bx" << e << " = true;\n";
+                if (g.two_domains)
+                    for (int e = 0; e < V; ++e) o << "      const bool act" << e << " = true;\n";
+                return;
+            }
+            for (int e = 0; e < V; ++e)
+                o << "      const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
+                  << " < xhi);\n";
+            if (g.two_domains) {
+                std::ostringstream rowin;
+                rowin << "true";
+                if (N == 2) rowin << " & (y >= a.rlo[0]) & (y < a.rhi[0])";
+                if (N == 3)
+                    rowin << " & (z >= a.rlo[0]) & (z < a.rhi[0]) & (y >= a.rlo[1]) & (y < a.rhi[1])";
+                o << "      const bool rowin = " << rowin.str() << ";\n";
+                for (int e = 0; e < V; ++e)
+                    o << "      const bool act" << e << " = rowin & (x + " << e << " >= rxlo) & (x + "
+                      << e << " < rxhi);\n";
+            }
+        };
+        auto emit_rows = [&](bool fast) {
             o << "#pragma unroll\n";
             o << "    for (int r = 0; r < CN_R; ++r) {\n";
-            o << "      const long long x = xbase + ((long long)tile * CN_R + r) * (CN_BLOCK * " << V
-              << ") + threadIdx.x * " << V << ";\n";
-            o << "      const long long p = x;\n";
+            if (N == 1) {
+                o << "      const long long x = t0 + (long long)r * (CN_BLOCK * " << V
+                  << ") + threadIdx.x * " << V << ";\n";
+                o << "      const long long p = x;\n";
+            } else {
+                o << "      const long long y = ybase + r;\n";
+                if (!fast) o << "      if (y >= a.hi[" << (N - 2) << "]) break;\n";
+                if (N == 2) o << "      const long long p = y * s0 + x;\n";
+                else o << "      const long long p = z * s0 + y * s1 + x;\n";
+            }
+            emit_guards(fast);
+            o << "      if " << guard_any(DOM_BOX) << " {\n";
+            shifted_body("        ");
+            o << "      }\n";
+            o << "    }\n";
+        };
+        const char* ilo = g.two_domains ? "rxlo" : "xlo";
+        const char* ihi = g.two_domains ? "rxhi" : "xhi";
+        if (N == 1) {
+            o << "  for (unsigned int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+            o << "    const long long t0 = xbase + (long long)tile * (CN_R * CN_BLOCK * " << V << ");\n";
+            o << "    const bool interior = (t0 >= " << ilo << ") & (t0 + CN_R * CN_BLOCK * " << V
+              << " <= " << ihi << ");\n";
         } else {
             o << "  const unsigned int ntx = (unsigned int)a.ntx;\n";
             if (N == 3) o << "  const unsigned int nty = (unsigned int)a.nty;\n";
@@ -349,34 +425,209 @@ struct Gen {
             } else {
                 o << "    const unsigned int ty = t2;\n";
             }
-            o << "    const long long x = xbase + ((long long)tx * CN_TX + lx) * " << V << ";\n";
-            o << "    const long long ybase = a.lo[" << (N - 2) << "] + ((long long)ty * (CN_BLOCK / CN_TX) + ly) * CN_R;\n";
-            o << "#pragma unroll\n";
-            o << "    for (int r = 0; r < CN_R; ++r) {\n";
-            o << "      const long long y = ybase + r;\n";
-            o << "      if (y >= a.hi[" << (N - 2) << "]) break;\n";
-            if (N == 2) o << "      const long long p = y * s0 + x;\n";
-            else o << "      const long long p = z * s0 + y * s1 + x;\n";
+            o << "    const long long tx0 = xbase + (long long)tx * (CN_TX * " << V << ");\n";
+            o << "    const long long ty0 = a.lo[" << (N - 2) << "] + (long long)ty * ((CN_BLOCK / CN_TX) * CN_R);\n";
+            o << "    const long long x = tx0 + lx * " << V << ";\n";
+            o << "    const long long ybase = ty0 + ly * CN_R;\n";
+            const std::string dom = g.two_domains ? "a.rlo" : "a.lo";
+            const std::string domh = g.two_domains ? "a.rhi" : "a.hi";
+            o << "    const bool interior = (tx0 >= " << ilo << ") & (tx0 + CN_TX * " << V << " <= " << ihi
+              << ") & (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + (CN_BLOCK / CN_TX) * CN_R <= "
+              << domh << "[" << (N - 2) << "])";
+            if (N == 3 && g.two_domains) o << " & (z >= a.rlo[0]) & (z < a.rhi[0])";
+            o << ";\n";
         }
-        for (int e = 0; e < V; ++e)
-            o << "      const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
-              << " < xhi);\n";
-        if (g.two_domains) {
-            std::ostringstream rowin;
-            rowin << "true";
-            if (N == 2) rowin << " & (y >= a.rlo[0]) & (y < a.rhi[0])";
-            if (N == 3)
-                rowin << " & (z >= a.rlo[0]) & (z < a.rhi[0]) & (y >= a.rlo[1]) & (y < a.rhi[1])";
-            o << "      const bool rowin = " << rowin.str() << ";\n";
-            for (int e = 0; e < V; ++e)
-                o << "      const bool act" << e << " = rowin & (x + " << e << " >= rxlo) & (x + "
-                  << e << " < rxhi);\n";
-        }
-        o << "      if " << guard_any(DOM_BOX) << " {\n";
-        shifted_body("        ");
-        o << "      }\n";
+        o << "    if (interior) {\n";
+        emit_rows(true);
+        o << "    } else {\n";
+        emit_rows(false);
         o << "    }\n";
         o << "  }\n";
+        red_epilogue();
+        o << "}\n";
+    }
+
+    // ---- SHIFTED class, staged variant -----------------------------------------------------
+    // The array that is read at shifted positions is brought into shared memory by the TMA
+    // unit: 2-D groups fetch one (rows + 2 hy) x (cols + 4) tile per stage and keep three
+    // stages in flight along the block's list of tiles; 3-D groups march along dimension 0
+    // through a ring of plane tiles, so every plane is fetched once per column of tiles
+    // instead of once per stencil arm.  One elected thread issues the copies; an mbarrier per
+    // slot counts the bytes; all waits are bounded.  Everything else (other inputs, outputs,
+    // reductions) goes through the same code as the cache-served variant.
+    void staged() {
+        const int N = g.ndims;
+        const int V = 2;
+        staged_mode = true;
+        prologue();
+        scalar_outs();
+        for (auto& l : g.leaves) in_slot(l.name);
+        const bool inplace = any_inplace();
+        for (size_t i = 0; i < in_names.size(); ++i) {
+            bool alias = inplace && aliases_written_buffer(in_names[i]);
+            o << "  const T* " << (alias ? "" : "__restrict__ ") << "in" << i << " = (const T*)a.in["
+              << i << "];\n";
+        }
+        for (size_t m = 0; m < g.outs.size(); ++m) {
+            bool shadow = g.copy_through && g.outs[m].hazard;
+            o << "  T* " << (shadow ? "__restrict__ " : "") << "out" << m << " = (T*)a.out[" << m
+              << "];\n";
+            if (g.outs[m].needs_old)
+                o << "  const T* old" << m << " = (const T*)a.old[" << m << "];\n";
+        }
+        red_decl();
+        const int L = N - 1;
+        const int NS = N == 3 ? 2 * g.hz + 3 : 3;
+        o << "  enum { CN_HY = " << g.hy << ", CN_HZ = " << g.hz << ", CN_NS = " << NS
+          << ", CN_TXE = CN_TX * 2, CN_SW = CN_TXE + 4, CN_TYT = (CN_BLOCK / CN_TX) * CN_R, "
+             "CN_SH = CN_TYT + 2 * CN_HY, CN_BOX = CN_SH * CN_SW, CN_SLOT = (CN_BOX + 15) / 16 * 16 };\n";
+        o << "  extern __shared__ __align__(128) unsigned char cn_dyn[];\n";
+        o << "  T* const ring = (T*)cn_dyn;\n";
+        o << "  unsigned long long* const full = (unsigned long long*)(cn_dyn + (size_t)CN_NS * CN_SLOT * sizeof(T));\n";
+        o << "  if (threadIdx.x == 0) {\n";
+        o << "    for (int s = 0; s < CN_NS; ++s) cn_mbar_init(&full[s], 1u);\n";
+        o << "    cn_mbar_init_fence();\n";
+        o << "  }\n";
+        o << "  __syncthreads();\n";
+        o << "  const long long s0 = a.stride[0];\n";
+        if (N == 3) o << "  const long long s1 = a.stride[1];\n";
+        o << "  const long long xlo = a.lo[" << L << "], xhi = a.hi[" << L << "];\n";
+        if (g.two_domains)
+            o << "  const long long rxlo = a.rlo[" << L << "], rxhi = a.rhi[" << L << "];\n";
+        o << "  const long long xbase = xlo & ~1LL;\n";
+        o << "  const unsigned int ntiles = (unsigned int)a.ntiles;\n";
+        o << "  const unsigned int ntx = (unsigned int)a.ntx;\n";
+        if (N == 3) o << "  const unsigned int nty = (unsigned int)a.nty;\n";
+        o << "  const int lx = threadIdx.x % CN_TX, ly = threadIdx.x / CN_TX;\n";
+        o << "  bool timed_out = false;\n";
+        const char* ilo = g.two_domains ? "rxlo" : "xlo";
+        const char* ihi = g.two_domains ? "rxhi" : "xhi";
+        const std::string dom = g.two_domains ? "a.rlo" : "a.lo";
+        const std::string domh = g.two_domains ? "a.rhi" : "a.hi";
+
+        auto emit_guards = [&](bool fast) {
+            if (fast) {
+                for (int e = 0; e < V; ++e) o << "        const bool bx" << e << " = true;\n";
+                if (g.two_domains)
+                    for (int e = 0; e < V; ++e) o << "        const bool act" << e << " = true;\n";
+                return;
+            }
+            for (int e = 0; e < V; ++e)
+                o << "        const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
+                  << " < xhi);\n";
+            if (g.two_domains) {
+                std::ostringstream rowin;
+                rowin << "true";
+                if (N == 2) rowin << " & (y >= a.rlo[0]) & (y < a.rhi[0])";
+                if (N == 3)
+                    rowin << " & (z >= a.rlo[0]) & (z < a.rhi[0]) & (y >= a.rlo[1]) & (y < a.rhi[1])";
+                o << "        const bool rowin = " << rowin.str() << ";\n";
+                for (int e = 0; e < V; ++e)
+                    o << "        const bool act" << e << " = rowin & (x + " << e
+                      << " >= rxlo) & (x + " << e << " < rxhi);\n";
+            }
+        };
+        auto emit_rows = [&](bool fast) {
+            o << "#pragma unroll\n";
+            o << "      for (int r = 0; r < CN_R; ++r) {\n";
+            o << "        const long long y = ybase + r;\n";
+            if (!fast) o << "        if (y >= a.hi[" << (N - 2) << "]) break;\n";
+            if (N == 2) o << "        const long long p = y * s0 + x;\n";
+            else o << "        const long long p = z * s0 + y * s1 + x;\n";
+            o << "        const int sq = (ly * CN_R + r + CN_HY) * CN_SW + lx * 2;\n";
+            emit_guards(fast);
+            o << "        if " << guard_any(DOM_BOX) << " {\n";
+            shifted_body("          ");
+            o << "        }\n";
+            o << "      }\n";
+        };
+        auto emit_interior = [&]() {
+            o << "      const bool interior = (tx0 >= " << ilo << ") & (tx0 + CN_TXE <= " << ihi
+              << ") & (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + CN_TYT <= " << domh << "["
+              << (N - 2) << "])";
+            if (N == 3 && g.two_domains) o << " & (z >= a.rlo[0]) & (z < a.rhi[0])";
+            o << ";\n";
+            o << "      if (interior) {\n";
+            emit_rows(true);
+            o << "      } else {\n";
+            emit_rows(false);
+            o << "      }\n";
+        };
+
+        if (N == 2) {
+            // tile k of this block: index blockIdx.x + k * gridDim.x, slot k % CN_NS
+            o << "  const unsigned int nmine = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;\n";
+            o << "  auto issue = [&](unsigned int k) {\n";
+            o << "    const unsigned int tile = blockIdx.x + k * gridDim.x;\n";
+            o << "    const long long fx = xbase + (long long)(tile % ntx) * CN_TXE - 2 + a.tm_off[1];\n";
+            o << "    const long long fy = a.lo[0] + (long long)(tile / ntx) * CN_TYT - CN_HY + a.tm_off[0];\n";
+            o << "    const unsigned int s = k % CN_NS;\n";
+            o << "    cn_mbar_expect_tx(&full[s], (unsigned int)(CN_BOX * sizeof(T)));\n";
+            o << "    cn_tma_load_2d(ring + (size_t)s * CN_SLOT, a.tmap, (int)fx, (int)fy, &full[s]);\n";
+            o << "  };\n";
+            o << "  if (threadIdx.x == 0)\n";
+            o << "    for (unsigned int k = 0; k < nmine && k < CN_NS; ++k) issue(k);\n";
+            o << "  for (unsigned int k = 0; k < nmine; ++k) {\n";
+            o << "    const unsigned int tile = blockIdx.x + k * gridDim.x;\n";
+            o << "    const unsigned int slot = k % CN_NS;\n";
+            // the verdict of the bounded wait is made block-uniform, so that no thread can
+            // leave the loop while others go on to the barrier below
+            o << "    const bool ok = cn_mbar_wait(&full[slot], (k / CN_NS) & 1u);\n";
+            o << "    if (__syncthreads_or(ok ? 0 : 1)) { timed_out = true; break; }\n";
+            o << "    {\n";
+            o << "      const T* const sp0 = ring + (size_t)slot * CN_SLOT;\n";
+            o << "      const unsigned int tx = tile % ntx, ty = tile / ntx;\n";
+            o << "      const long long tx0 = xbase + (long long)tx * CN_TXE;\n";
+            o << "      const long long ty0 = a.lo[0] + (long long)ty * CN_TYT;\n";
+            o << "      const long long x = tx0 + lx * 2;\n";
+            o << "      const long long ybase = ty0 + ly * CN_R;\n";
+            emit_interior();
+            o << "    }\n";
+            o << "    __syncthreads();\n";
+            o << "    if (threadIdx.x == 0 && k + CN_NS < nmine) issue(k + CN_NS);\n";
+            o << "  }\n";
+        } else {
+            // march along dimension 0 in chunks; plane i of a chunk is (zs - hz + i), and the
+            // running load counter `gs` picks its slot and the parity of its barrier phase
+            o << "  unsigned int gs = 0;\n";
+            o << "  for (unsigned int tile = blockIdx.x; tile < ntiles && !timed_out; tile += gridDim.x) {\n";
+            o << "    const unsigned int tx = tile % ntx; const unsigned int t2 = tile / ntx;\n";
+            o << "    const unsigned int ty = t2 % nty; const unsigned int zc = t2 / nty;\n";
+            o << "    const long long tx0 = xbase + (long long)tx * CN_TXE;\n";
+            o << "    const long long ty0 = a.lo[1] + (long long)ty * CN_TYT;\n";
+            o << "    const long long zs = a.lo[0] + (long long)zc * a.zchunk;\n";
+            o << "    const long long ze = zs + a.zchunk < a.hi[0] ? zs + a.zchunk : a.hi[0];\n";
+            o << "    const unsigned int total = (unsigned int)(ze - zs) + 2 * CN_HZ;\n";
+            o << "    const long long x = tx0 + lx * 2;\n";
+            o << "    const long long ybase = ty0 + ly * CN_R;\n";
+            o << "    auto issue = [&](unsigned int i) {\n";
+            o << "      const unsigned int s = (gs + i) % CN_NS;\n";
+            o << "      cn_mbar_expect_tx(&full[s], (unsigned int)(CN_BOX * sizeof(T)));\n";
+            o << "      cn_tma_load_3d(ring + (size_t)s * CN_SLOT, a.tmap, (int)(tx0 - 2 + a.tm_off[2]), "
+                 "(int)(ty0 - CN_HY + a.tm_off[1]), (int)(zs - CN_HZ + (long long)i + a.tm_off[0]), &full[s]);\n";
+            o << "    };\n";
+            o << "    if (threadIdx.x == 0)\n";
+            o << "      for (unsigned int i = 0; i < total && i < CN_NS; ++i) issue(i);\n";
+            o << "    unsigned int waited = 0;\n";
+            o << "    for (long long z = zs; z < ze; ++z) {\n";
+            o << "      const unsigned int i0 = (unsigned int)(z - zs);\n";
+            o << "      while (waited <= i0 + 2 * CN_HZ) {\n";
+            o << "        const bool ok = cn_mbar_wait(&full[(gs + waited) % CN_NS], ((gs + waited) / CN_NS) & 1u);\n";
+            o << "        if (__syncthreads_or(ok ? 0 : 1)) { timed_out = true; break; }\n";
+            o << "        ++waited;\n";
+            o << "      }\n";
+            o << "      if (timed_out) break;\n";
+            for (int d = 0; d <= 2 * g.hz; ++d)
+                o << "      const T* const sp" << d << " = ring + (size_t)((gs + i0 + " << d
+                  << ") % CN_NS) * CN_SLOT;\n";
+            emit_interior();
+            o << "      __syncthreads();\n";
+            o << "      if (threadIdx.x == 0 && i0 + CN_NS < total) issue(i0 + CN_NS);\n";
+            o << "    }\n";
+            o << "    gs += total;\n";
+            o << "  }\n";
+        }
+        o << "  if (timed_out && a.error) atomicExch(a.error, 1u);\n";
         red_epilogue();
         o << "}\n";
     }
@@ -446,7 +697,10 @@ int generate_source(const GroupIR& g, std::string* src, std::string* err) {
     Gen gen{g, {}, {}};
     switch (g.cls) {
         case GroupIR::SCALAR_ONLY: gen.scalar_only(); break;
-        case GroupIR::SHIFTED: gen.shifted(); break;
+        case GroupIR::SHIFTED:
+            if (g.staged) gen.staged();
+            else gen.shifted();
+            break;
         case GroupIR::STRIDED: gen.strided(); break;
         default:
             if (err) *err = "unknown group class";

@@ -25,6 +25,13 @@ Context::Context(int device, int rank, int nranks)
         }
     }
     if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
+    if (const char* t = getenv("CN_STAGED_TILE")) {
+        int tx = 0, r = 0;
+        if (sscanf(t, "%d,%d", &tx, &r) == 2 && tx >= 8 && tx <= 64 && (256 % tx) == 0 && r >= 1 && r <= 16) {
+            staged_tile_.tx = tx;
+            staged_tile_.r = r;
+        }
+    }
 }
 
 Context::~Context() {
@@ -114,6 +121,9 @@ int Context::init() {
     CN_DRV(LaunchKernel, "cuLaunchKernel")
     CN_DRV(GetErrorString, "cuGetErrorString")
     CN_DRV(OccupancyMaxActiveBlocksPerMultiprocessor, "cuOccupancyMaxActiveBlocksPerMultiprocessor")
+    CN_DRV(FuncSetAttribute, "cuFuncSetAttribute")
+    CN_DRV(TensorMapEncodeTiled, "cuTensorMapEncodeTiled")
+    error_word_ = counter_ + 16;  // second cache line of the zeroed 256-byte scratch block
 #undef CN_DRV
     initialised_ = true;
     return CN_OK;
@@ -126,10 +136,16 @@ Array* Context::find(int name) {
     return it == arrays_.end() ? nullptr : &it->second;
 }
 
+// Slab partition of dimension 0: ceil(n0 / nranks) consecutive rows per rank, the last
+// non-empty rank takes the remainder, ranks beyond it own nothing.
+void slab_partition(int64_t n0, int nranks, int rank, int64_t* begin, int64_t* end) {
+    int64_t per = (n0 + nranks - 1) / nranks;
+    *begin = std::min<int64_t>((int64_t)rank * per, n0);
+    *end = std::min<int64_t>((int64_t)(rank + 1) * per, n0);
+}
+
 void Context::partition(int64_t n0, int64_t* begin, int64_t* end, int r) const {
-    int64_t per = (n0 + nranks_ - 1) / nranks_;
-    *begin = std::min<int64_t>((int64_t)r * per, n0);
-    *end = std::min<int64_t>((int64_t)(r + 1) * per, n0);
+    slab_partition(n0, nranks_, r, begin, end);
 }
 
 int Context::alloc_buffer(const Array& a, Buffer* b) {

@@ -54,6 +54,8 @@ struct CompiledGroup {
     CUfunction func = nullptr;
     int blocks_per_sm = 1;  // resident 256-thread blocks per SM, from the occupancy query
     std::string label;      // short description used by the profile report
+    TileConfig tile;        // tile shape the kernel was compiled for
+    size_t smem_bytes = 0;  // dynamic shared memory (staged kernels)
     std::string source;
     std::string log;
 };
@@ -61,6 +63,7 @@ struct CompiledGroup {
 struct Stats {
     long long kernel_launches = 0;   // kernels of this library launched (AOT + generated)
     long long group_launches = 0;    // of which generated group kernels
+    long long staged_launches = 0;   // of which TMA-staged stencil kernels
     long long compiles = 0;          // NVRTC compilations (cache misses)
     long long halo_exchanges = 0;
     long long allreduces = 0;
@@ -77,7 +80,14 @@ struct DriverApi {
                              unsigned, CUstream, void**, void**) = nullptr;
     CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
     CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
+    CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                     CUtensorMapFloatOOBfill) = nullptr;
 };
+
+void slab_partition(int64_t n0, int nranks, int rank, int64_t* begin, int64_t* end);
 
 class Context {
 public:
@@ -117,6 +127,10 @@ public:
         if (tx > 0) tile_.tx = tx;
         if (r > 0) tile_.r = r;
     }
+    void set_staged_tile(int tx, int r) {
+        if (tx > 0) staged_tile_.tx = tx;
+        if (r > 0) staged_tile_.r = r;
+    }
 
 private:
     int fail(int code, const std::string& msg);
@@ -153,6 +167,8 @@ private:
     int try_plain_fill(const DagNode& node, bool* done);
     int exchange_halo(Array* a);
     int ensure_scratch(size_t bytes);
+    int encode_tensor_map(const Array& x, const CompiledGroup& k, const GroupIR& g, CnGroupArgs* a);
+    int check_device_error();
     int operand_array(const Operand& op, Array** out, Region* region);
 
     int device_, rank_, nranks_;
@@ -166,6 +182,9 @@ private:
     std::vector<bool> failed_;
     DriverApi drv_;
     TileConfig tile_;
+    TileConfig staged_tile_;   // tile shape of the TMA-staged stencil kernels
+    unsigned int* error_word_ = nullptr;  // set by a kernel whose bounded wait ran out
+    long long staged_checked_ = 0;        // staged launches already covered by an error check
 
     std::unordered_map<int, Array> arrays_;
     std::unordered_map<std::string, CompiledGroup> kernels_;

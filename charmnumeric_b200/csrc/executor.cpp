@@ -24,21 +24,29 @@ void array_strides(const Array& a, int64_t* s) {
 }  // namespace
 
 int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
-    std::string key = g.key() + "|T" + std::to_string(tile_.tx) + "," + std::to_string(tile_.r);
+    TileConfig tile = tile_;
+    if (g.staged) {
+        // a staged tile is one TMA box: at most 256 elements per side
+        tile = staged_tile_;
+        if (tile.tx > 64) tile.tx = 64;
+        while ((CN_BLOCK / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
+    }
+    std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r);
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
         return CN_OK;
     }
     CompiledGroup k;
+    k.tile = tile;
     int rc = generate_source(g, &k.source, &err_);
     if (rc) return rc;
     std::vector<char> cubin;
-    rc = nvrtc_compile(k.source, tile_, &cubin, &k.log);
+    rc = nvrtc_compile(k.source, tile, &cubin, &k.log);
     if (rc) return fail(rc, "group kernel failed to compile:\n" + k.log);
     stats_.compiles++;
     if ((rc = driver_fail(drv_.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData"))) return rc;
-    if ((rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, "cn_group"), "cuModuleGetFunction"))) return rc;
+    if ((rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, g.entry_name().c_str()), "cuModuleGetFunction"))) return rc;
     {
         const char* cls = g.cls == GroupIR::SHIFTED ? (g.flat ? "flat" : "shifted")
                           : (g.cls == GroupIR::STRIDED ? "strided" : "scalar");
@@ -48,8 +56,18 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
                  g.copy_through ? " copy-through" : "");
         k.label = lbl;
     }
+    if (g.staged) {
+        const int ns = g.ndims == 3 ? 2 * g.hz + 3 : 3;
+        const size_t sw = (size_t)tile.tx * 2 + 4, sh = (size_t)(CN_BLOCK / tile.tx) * tile.r + 2 * g.hy;
+        const size_t slot = (sh * sw + 15) / 16 * 16;
+        k.smem_bytes = ns * slot * sizeof(double) + ns * sizeof(unsigned long long);
+        k.label += " tma";
+        if ((rc = driver_fail(drv_.FuncSetAttribute(k.func, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                                    (int)k.smem_bytes), "cuFuncSetAttribute")))
+            return rc;
+    }
     int occ = 0;
-    if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, CN_BLOCK, 0) == CUDA_SUCCESS && occ > 0)
+    if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, CN_BLOCK, k.smem_bytes) == CUDA_SUCCESS && occ > 0)
         k.blocks_per_sm = occ;
     auto ins = kernels_.emplace(key, std::move(k));
     *out = &ins.first->second;
@@ -106,13 +124,15 @@ int Context::profile_report(char* buf, int64_t cap) {
 int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes) {
     void* params[] = {(void*)&a};
     prof_start(k->label, bytes);
-    int rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, 0,
+    int rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1,
+                                           (unsigned)k->smem_bytes,
                                            (CUstream)stream_, params, nullptr),
                          "cuLaunchKernel");
     prof_stop();
     if (rc) return rc;
     stats_.kernel_launches++;
     stats_.group_launches++;
+    if (k->smem_bytes) stats_.staged_launches++;
     return CN_OK;
 }
 
@@ -133,6 +153,49 @@ int Context::run_group(const GroupIR& g) {
         case GroupIR::STRIDED: return run_strided(g, k);
     }
     return fail(CN_ERR_UNSUPPORTED, "unknown group class");
+}
+
+// TMA descriptor of the stencil array's local slab (halo rows included), box = one tile.
+int Context::encode_tensor_map(const Array& x, const CompiledGroup& k, const GroupIR& g, CnGroupArgs* a) {
+    const int nd = x.ndims;
+    const size_t esz = sizeof(double);
+    cuuint64_t dims[3] = {1, 1, 1};
+    cuuint64_t strides[2] = {0, 0};
+    cuuint32_t box[3] = {1, 1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const cuuint64_t rows0 = (cuuint64_t)(x.local_rows() + 2 * x.halo);
+    const cuuint32_t sw = (cuuint32_t)k.tile.tx * 2 + 4;
+    const cuuint32_t sh = (cuuint32_t)(CN_BLOCK / k.tile.tx) * k.tile.r + 2 * g.hy;
+    if (nd == 2) {
+        dims[0] = (cuuint64_t)x.shape[1];
+        dims[1] = rows0;
+        strides[0] = (cuuint64_t)x.shape[1] * esz;
+        box[0] = sw;
+        box[1] = sh;
+    } else {
+        dims[0] = (cuuint64_t)x.shape[2];
+        dims[1] = (cuuint64_t)x.shape[1];
+        dims[2] = rows0;
+        strides[0] = (cuuint64_t)x.shape[2] * esz;
+        strides[1] = (cuuint64_t)x.shape[2] * x.shape[1] * esz;
+        box[0] = sw;
+        box[1] = sh;
+        box[2] = 1;
+    }
+    if (rows0 == 0) dims[nd - 1] = 1;
+    char* base = x.buf.data - (size_t)x.halo * x.unit * esz;
+    CUtensorMap tm;
+    CUresult r = drv_.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, (cuuint32_t)nd, base, dims, strides,
+                                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    int rc = driver_fail(r, "cuTensorMapEncodeTiled");
+    if (rc) return rc;
+    static_assert(sizeof(CUtensorMap) == 128, "descriptor size");
+    memcpy(a->tmap, &tm, sizeof(tm));
+    a->tm_off[0] = x.halo;
+    a->tm_off[1] = 0;
+    a->tm_off[2] = 0;
+    return CN_OK;
 }
 
 // Size-1 inputs and outputs.  An output whose array is also read as an input of the same
@@ -298,7 +361,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         a.hi[0] = n;
         a.rlo[0] = 0;
         a.rhi[0] = n;
-        int64_t per = (int64_t)tile_.r * CN_BLOCK * V;
+        int64_t per = (int64_t)k->tile.r * CN_BLOCK * V;
         ntiles = (n + per - 1) / per;
     } else {
         for (int d = 0; d < nd; ++d) {
@@ -314,20 +377,38 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
             const int L = nd - 1;
             int64_t xbase = V == 2 ? (lo[L] & ~1LL) : lo[L];
             if (nd == 1) {
-                int64_t per = (int64_t)tile_.r * CN_BLOCK * V;
+                int64_t per = (int64_t)k->tile.r * CN_BLOCK * V;
                 ntiles = (hi[0] - xbase + per - 1) / per;
             } else {
-                int64_t ntx = (hi[L] - xbase + (int64_t)tile_.tx * V - 1) / ((int64_t)tile_.tx * V);
-                int64_t rows_per = (int64_t)(CN_BLOCK / tile_.tx) * tile_.r;
+                int64_t ntx = (hi[L] - xbase + (int64_t)k->tile.tx * V - 1) / ((int64_t)k->tile.tx * V);
+                int64_t rows_per = (int64_t)(CN_BLOCK / k->tile.tx) * k->tile.r;
                 int64_t nty = (hi[nd - 2] - lo[nd - 2] + rows_per - 1) / rows_per;
                 int64_t nz = nd == 3 ? hi[0] - lo[0] : 1;
                 a.ntx = ntx;
                 a.nty = nty;
-                ntiles = ntx * nty * nz;
+                if (g.staged && nd == 3) {
+                    // chunks of dimension 0: enough tiles to balance the persistent blocks,
+                    // long enough that the 2*hz planes of run-in stay cheap
+                    int64_t want = 4LL * sm_count_ * k->blocks_per_sm;
+                    int64_t nzc = std::max<int64_t>(1, (want + ntx * nty - 1) / (ntx * nty));
+                    int64_t zchunk = std::max<int64_t>(std::min<int64_t>(nz, 32), (nz + nzc - 1) / nzc);
+                    nzc = (nz + zchunk - 1) / zchunk;
+                    a.nzc = nzc;
+                    a.zchunk = zchunk;
+                    ntiles = ntx * nty * nzc;
+                } else {
+                    ntiles = ntx * nty * nz;
+                }
             }
         }
     }
     if (ntiles >= (1LL << 31)) return fail(CN_ERR_LIMIT, "too many tiles for one launch");
+    if (g.staged) {
+        Array* sx = find(g.stage_array);
+        if (!sx) return fail(CN_ERR_UNKNOWN_ARRAY, "stencil array vanished");
+        if ((rc = encode_tensor_map(*sx, *k, g, &a))) return rc;
+        a.error = error_word_;
+    }
     a.ntiles = ntiles;
     int grid = (int)std::min<int64_t>(std::max<int64_t>(ntiles, 1), (int64_t)sm_count_ * k->blocks_per_sm);
 
@@ -651,7 +732,24 @@ int Context::execute_randu(const AstNode& r) {
 
 int Context::synchronize() {
     if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
-    return cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    int rc = cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    if (rc) return rc;
+    return check_device_error();
+}
+
+// A staged kernel whose bounded wait on a tile ran out leaves 1 in the error word.
+int Context::check_device_error() {
+    if (stats_.staged_launches == staged_checked_) return CN_OK;
+    staged_checked_ = stats_.staged_launches;
+    unsigned int word = 0;
+    int rc = cuda_fail(cudaMemcpyAsync(&word, error_word_, sizeof(word), cudaMemcpyDeviceToHost, stream_), "error word");
+    if (rc) return rc;
+    if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize"))) return rc;
+    if (word) {
+        cudaMemsetAsync(error_word_, 0, sizeof(word), stream_);
+        return fail(CN_ERR_CUDA, "a stencil kernel gave up waiting for a tile copy (results are incomplete)");
+    }
+    return CN_OK;
 }
 
 int Context::get(int name, int64_t count, int dtype, void* out) {

@@ -79,6 +79,11 @@ struct GroupIR {
     bool flat = false;          // SHIFTED with zero deltas over whole arrays: 1-D walk
     int vec = 1;                // elements per thread along the last dimension
     int max_halo = 0;           // SHIFTED: largest |delta| along dimension 0
+    // Staged variant (2-D / 3-D float64 stencils): the one array that is read at shifted
+    // positions is fetched tile by tile into shared memory by the TMA unit.
+    bool staged = false;
+    int stage_array = -1;       // name of that array
+    int hy = 0, hz = 0;         // halo rows / planes a tile carries on each side
 
     std::vector<LeafIR> leaves;
     std::vector<double> scalars;
@@ -90,6 +95,9 @@ struct GroupIR {
 
     // Structural key: equal keys <=> identical generated source.
     std::string key() const;
+    // Name of the kernel entry point: class, rank and operand counts in clear plus a hash of
+    // the key, so that a profiler's kernel filter can pick one group kernel.
+    std::string entry_name() const;
     // SHIFTED class: distinct input arrays in order of first use; slot i of the launch
     // arguments' `in[]` is array input_arrays()[i].  STRIDED class: one slot per leaf.
     std::vector<int> input_arrays() const;
@@ -102,7 +110,12 @@ struct GroupIR {
 int lower_group(const DagNode& node, const std::vector<const AstNode*>& fused, GroupIR* out,
                 std::string* err, bool force_strided = false);
 
-// Emit the CUDA source of the group kernel (entry point "cn_group").
+// Shared-memory / TMA staging of stencil groups: on by default, CN_STAGED=0 or
+// cn_set_option(ctx, "staged", 0) switches back to the cache-served kernels.
+void set_staged_enabled(bool on);
+bool staged_enabled();
+
+// Emit the CUDA source of the group kernel (entry point g.entry_name()).
 int generate_source(const GroupIR& g, std::string* src, std::string* err);
 
 }  // namespace cn

@@ -12,6 +12,8 @@
 // common shape: stencils and plain elementwise chains) and the general "strided" class,
 // hazard detection for in-place SET_REGION, and REDUCE / SUM roots fused behind the group.
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <sstream>
@@ -69,6 +71,7 @@ struct Lowering {
     std::map<int, int> out_by_name;   // array name -> outs index
     std::map<int, int> bc_by_name;
     bool force_strided = false;
+    bool allow_staged = true;
 
     int fail(int code, const std::string& m) {
         if (err) *err = m;
@@ -678,6 +681,37 @@ struct Lowering {
         int esz = dtype_size(g.dtype);
         g.vec = 1;
         if (esz == 8 && (g.flat || nd == 1 || as[nd - 1] % 2 == 0)) g.vec = 2;
+        // staged variant: exactly one array is read at shifted positions, within a small halo
+        g.staged = false;
+        if (allow_staged && !g.flat && g.vec == 2 && g.dtype == DT_F64 && (nd == 2 || nd == 3)) {
+            int name = -1;
+            bool ok = true;
+            int hx = 0, hy = 0, hz = 0;
+            for (auto& l : g.leaves) {
+                bool shifted = l.delta[0] || l.delta[1] || l.delta[2];
+                if (!shifted) continue;
+                if (name >= 0 && name != l.name) ok = false;
+                name = l.name;
+            }
+            if (name >= 0 && ok) {
+                for (auto& l : g.leaves) {
+                    if (l.name != name) continue;
+                    auto mag = [](int64_t v) { return (int)(v < 0 ? -v : v); };
+                    hx = std::max(hx, mag(l.delta[nd - 1]));
+                    hy = std::max(hy, mag(l.delta[nd - 2]));
+                    if (nd == 3) hz = std::max(hz, mag(l.delta[0]));
+                }
+                // an in-place output on the stencil array would race with other tiles' fetches
+                for (auto& o : g.outs)
+                    if (o.name == name && !(copy_through && o.hazard)) ok = false;
+                if (ok && hx <= 2 && hy <= 2 && hz <= 1) {
+                    g.staged = true;
+                    g.stage_array = name;
+                    g.hy = hy;
+                    g.hz = hz;
+                }
+            }
+        }
         return true;
     }
 
@@ -774,9 +808,23 @@ void put(std::ostringstream& s, const ValRef& v) { s << (int)v.kind << ':' << v.
 
 }  // namespace
 
+namespace {
+int g_staged = -1;
+}
+
+void set_staged_enabled(bool on) { g_staged = on ? 1 : 0; }
+
+bool staged_enabled() {
+    if (g_staged < 0) {
+        const char* e = getenv("CN_STAGED");
+        g_staged = e ? (atoi(e) != 0 ? 1 : 0) : 1;
+    }
+    return g_staged != 0;
+}
+
 int lower_group(const DagNode& node, const std::vector<const AstNode*>& fused, GroupIR* out,
                 std::string* err, bool force_strided) {
-    Lowering l{node, *out, err, {}, {}, {}, {}, force_strided};
+    Lowering l{node, *out, err, {}, {}, {}, {}, force_strided, staged_enabled()};
     int rc = l.run(fused);
     if (rc) return rc;
     if ((int)out->leaves.size() > (out->cls == GroupIR::SHIFTED ? 32 : CN_MAX_IN)) {
@@ -796,10 +844,24 @@ std::vector<int> GroupIR::input_arrays() const {
     return names;
 }
 
+std::string GroupIR::entry_name() const {
+    const std::string k = key();
+    uint32_t h = 2166136261u;  // FNV-1a
+    for (unsigned char c : k) {
+        h ^= c;
+        h *= 16777619u;
+    }
+    const char* c = cls == SHIFTED ? (flat ? "flat" : "shifted") : (cls == STRIDED ? "strided" : "scalar");
+    char buf[128];
+    snprintf(buf, sizeof(buf), "cn_group_%s%dd_i%zuo%zur%zu%s_%08x", c, flat ? 1 : ndims,
+             input_arrays().size(), outs.size(), reds.size(), copy_through ? "_ct" : "", h);
+    return buf;
+}
+
 std::string GroupIR::key() const {
     std::ostringstream s;
     s << "c" << (int)cls << "t" << dtype << "n" << ndims << "v" << vec << "f" << flat << "d"
-      << two_domains << "x" << copy_through << "|L";
+      << two_domains << "x" << copy_through << "g" << staged << hy << hz << "|L";
     for (auto& l : leaves) {
         s << l.domain << ':';
         if (cls == SHIFTED) {

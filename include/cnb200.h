@@ -119,6 +119,12 @@ int cn_dag_check(const char* msg, int64_t size, int* n_nodes, int* n_roots, char
 int cn_group_compile_check(const char* node_blob, int64_t size, char* source, int64_t cap,
                            int64_t* cubin_bytes, char* err, int errcap);
 
+/* Rows [*begin, *end) of dimension 0 that `rank` of `nranks` owns for an array with n0 rows
+ * (host-only).  Takes the place of the reference's tile -> chare map
+ * (ArrayDecomp::owning_chare / chare_region_global, src/array_region.hpp:357-368): here one
+ * slab of ceil(n0 / nranks) consecutive rows per rank. */
+int cn_partition(int64_t n0, int nranks, int rank, int64_t* begin, int64_t* end);
+
 /* Device timing with CUDA events on the context's own stream. */
 int cn_timer_start(cn_context* ctx);
 int cn_timer_stop(cn_context* ctx, float* milliseconds);
@@ -146,7 +152,8 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
 
 /* Options: "halo" depth (rows per side, default 1; set before creating arrays),
  * "fuse_reductions" 0/1, "tile_tx" / "tile_rows" (shape of generated kernels: threads along
- * the last dimension, rows per thread), "profile" 0/1. */
+ * the last dimension, rows per thread), "staged" 0/1 (TMA / shared-memory staging of stencil
+ * tiles; process-wide), "staged_tile_tx" / "staged_tile_rows", "profile" 0/1. */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus

@@ -1,0 +1,71 @@
+"""Worker of the multi-GPU tests: one process per GPU.  Usage:
+    python tests/multi_worker.py <rank> <nranks> <id-file> <out-dir> <case>
+Rank 0 writes the 128-byte communicator id to <id-file>; the others wait for it."""
+import os
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+
+import charmnumeric_b200 as cnp  # noqa: E402
+from charmnumeric_b200 import frontend as F  # noqa: E402
+from oracle.oracle import Oracle  # noqa: E402
+from tests import test_gpu_parity as G  # noqa: E402
+
+
+def main():
+    rank, nranks, idfile, outdir, case = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[5]
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if rank == 0:
+        uid = cnp.comm_unique_id()
+        tmp = idfile + ".tmp"
+        Path(tmp).write_bytes(uid)
+        os.replace(tmp, idfile)
+    else:
+        t0 = time.time()
+        while not os.path.exists(idfile):
+            if time.time() - t0 > 120:
+                raise SystemExit("timed out waiting for the communicator id")
+            time.sleep(0.05)
+        uid = Path(idfile).read_bytes()
+    itf = cnp.CharmNumericInterface(device=rank, rank=rank, nranks=nranks, unique_id=uid)
+    progs = {
+        "jacobi2d": G._jacobi2d_program(67, 130, 6, res_every=3),
+        "jacobi2d_small": G._jacobi2d_program(9, 8, 3),
+        "jacobi3d": G._jacobi3d_program((19, 12, 34), 3),
+        "cg": G._cg_poisson_program(34, 8),
+    }
+
+    def chain():
+        a = cnp.random.uniform((100003,), seed=2, low=-1.0, high=1.0)
+        b = cnp.random.uniform((100003,), seed=3, low=-1.0, high=1.0)
+        return {"r": G._chain(a, b), "s": cnp.sum(G._chain(a, b)), "d": cnp.dot2d(a, b)}
+
+    def matvec():
+        A = cnp.random.uniform((301, 128), seed=21, low=-1.0, high=1.0)
+        x = cnp.random.uniform((128,), seed=22, low=-1.0, high=1.0)
+        y = A @ x
+        return {"y": y, "n": y @ y}
+    progs["chain"] = chain
+    progs["matvec"] = matvec
+    cnp.reset_frontend_state()
+    outs = progs[case]()
+    orc = Oracle()
+    F.execute(itf, mirror=orc)
+    result = {}
+    for k, v in outs.items():
+        result["gpu_" + k] = itf.context.get(v.name).reshape(v.shape)
+        result["cpu_" + k] = np.array(orc.get(v.name)).reshape(v.shape)
+    st = itf.context.stats()
+    result["halo_exchanges"] = np.array(st["halo_exchanges"])
+    result["allreduces"] = np.array(st["allreduces"])
+    np.savez(os.path.join(outdir, f"{case}_rank{rank}.npz"), **result)
+    itf.close()
+
+
+if __name__ == "__main__":
+    main()
