@@ -172,6 +172,10 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
     std::vector<char> cubin;
     std::string log;
     cn::TileConfig tile;
+    if (g.staged) {  // a staged tile is one TMA box
+        tile.tx = 64;
+        tile.r = 4;
+    }
     rc = cn::nvrtc_compile(src, tile, &cubin, &log);
     if (rc) {
         copy_err(log, err, errcap);
@@ -225,7 +229,7 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         if (value < 0 || value > 8) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_halo((int)value);
     } else if (k == "staged") {
-        cn::set_staged_enabled(value != 0);
+        cn::set_staged_level((int)value);
     } else if (k == "staged_tile_tx") {
         if (value < 8 || value > 64 || 256 % value) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_staged_tile((int)value, -1);

@@ -355,8 +355,8 @@ struct Gen {
         }
         red_decl();
         const int L = N - 1;
-        if (N >= 2) o << "  const long long s0 = a.stride[0];\n";
-        if (N == 3) o << "  const long long s1 = a.stride[1];\n";
+        if (N >= 2) o << "  const long long s0 = CN_S0 ? CN_S0 : a.stride[0];\n";
+        if (N == 3) o << "  const long long s1 = CN_S1 ? CN_S1 : a.stride[1];\n";
         o << "  const long long xlo = a.lo[" << L << "], xhi = a.hi[" << L << "];\n";
         if (g.two_domains)
             o << "  const long long rxlo = a.rlo[" << L << "], rxhi = a.rhi[" << L << "];\n";
@@ -489,8 +489,8 @@ struct Gen {
         o << "    cn_mbar_init_fence();\n";
         o << "  }\n";
         o << "  __syncthreads();\n";
-        o << "  const long long s0 = a.stride[0];\n";
-        if (N == 3) o << "  const long long s1 = a.stride[1];\n";
+        o << "  const long long s0 = CN_S0 ? CN_S0 : a.stride[0];\n";
+        if (N == 3) o << "  const long long s1 = CN_S1 ? CN_S1 : a.stride[1];\n";
         o << "  const long long xlo = a.lo[" << L << "], xhi = a.hi[" << L << "];\n";
         if (g.two_domains)
             o << "  const long long rxlo = a.rlo[" << L << "], rxhi = a.rhi[" << L << "];\n";

@@ -25,6 +25,8 @@ Context::Context(int device, int rank, int nranks)
         }
     }
     if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
+    staged_tile_.tx = 64;
+    staged_tile_.r = 4;
     if (const char* t = getenv("CN_STAGED_TILE")) {
         int tx = 0, r = 0;
         if (sscanf(t, "%d,%d", &tx, &r) == 2 && tx >= 8 && tx <= 64 && (256 % tx) == 0 && r >= 1 && r <= 16) {

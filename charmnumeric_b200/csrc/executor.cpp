@@ -31,7 +31,13 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         if (tile.tx > 64) tile.tx = 64;
         while ((CN_BLOCK / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
     }
-    std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r);
+    if (g.cls == GroupIR::SHIFTED && !g.flat && g.ndims >= 2) {
+        // specialise on the element strides of the (common) array shape
+        tile.s0 = g.ndims == 2 ? g.array_shape[1] : g.array_shape[1] * g.array_shape[2];
+        tile.s1 = g.ndims == 3 ? g.array_shape[2] : 0;
+    }
+    std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
+                      std::to_string(tile.s0) + "," + std::to_string(tile.s1);
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;

@@ -110,10 +110,10 @@ struct GroupIR {
 int lower_group(const DagNode& node, const std::vector<const AstNode*>& fused, GroupIR* out,
                 std::string* err, bool force_strided = false);
 
-// Shared-memory / TMA staging of stencil groups: on by default, CN_STAGED=0 or
-// cn_set_option(ctx, "staged", 0) switches back to the cache-served kernels.
-void set_staged_enabled(bool on);
-bool staged_enabled();
+// Shared-memory / TMA staging of stencil groups.  Level 0: never; 1 (default): 3-D groups
+// only; 2: 2-D groups too.  Set with CN_STAGED or cn_set_option(ctx, "staged", level).
+void set_staged_level(int level);
+int staged_level();
 
 // Emit the CUDA source of the group kernel (entry point g.entry_name()).
 int generate_source(const GroupIR& g, std::string* src, std::string* err);

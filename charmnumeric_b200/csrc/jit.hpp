@@ -14,8 +14,11 @@
 namespace cn {
 
 struct TileConfig {
-    int tx = 64;  // threads along the last dimension
-    int r = 4;    // consecutive rows per thread
+    int tx = 256;  // threads along the last dimension
+    int r = 2;     // consecutive rows per thread
+    // element strides of the arrays a stencil kernel is specialised for (0: read at run time);
+    // as compile-time constants they turn every stencil arm into an immediate address offset
+    long long s0 = 0, s1 = 0;
 };
 
 // Compile CUDA source to a cubin image for sm_100a.  Works without a GPU.

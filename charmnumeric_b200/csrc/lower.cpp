@@ -683,7 +683,9 @@ struct Lowering {
         if (esz == 8 && (g.flat || nd == 1 || as[nd - 1] % 2 == 0)) g.vec = 2;
         // staged variant: exactly one array is read at shifted positions, within a small halo
         g.staged = false;
-        if (allow_staged && !g.flat && g.vec == 2 && g.dtype == DT_F64 && (nd == 2 || nd == 3)) {
+        const int level = staged_level();
+        if (allow_staged && (level == 2 || (level == 1 && nd == 3)) && !g.flat && g.vec == 2 &&
+            g.dtype == DT_F64 && (nd == 2 || nd == 3)) {
             int name = -1;
             bool ok = true;
             int hx = 0, hy = 0, hz = 0;
@@ -812,19 +814,21 @@ namespace {
 int g_staged = -1;
 }
 
-void set_staged_enabled(bool on) { g_staged = on ? 1 : 0; }
+void set_staged_level(int level) { g_staged = level < 0 ? 0 : (level > 2 ? 2 : level); }
 
-bool staged_enabled() {
+// 0: never, 1: 3-D stencils only (default: measured faster there, slower in 2-D), 2: always
+int staged_level() {
     if (g_staged < 0) {
         const char* e = getenv("CN_STAGED");
-        g_staged = e ? (atoi(e) != 0 ? 1 : 0) : 1;
+        g_staged = e ? atoi(e) : 1;
+        if (g_staged < 0 || g_staged > 2) g_staged = 1;
     }
-    return g_staged != 0;
+    return g_staged;
 }
 
 int lower_group(const DagNode& node, const std::vector<const AstNode*>& fused, GroupIR* out,
                 std::string* err, bool force_strided) {
-    Lowering l{node, *out, err, {}, {}, {}, {}, force_strided, staged_enabled()};
+    Lowering l{node, *out, err, {}, {}, {}, {}, force_strided, true};
     int rc = l.run(fused);
     if (rc) return rc;
     if ((int)out->leaves.size() > (out->cls == GroupIR::SHIFTED ? 32 : CN_MAX_IN)) {
