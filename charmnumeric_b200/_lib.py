@@ -61,6 +61,7 @@ SIGNATURES = {
     "cn_timer_start": (C.c_int, [_P]),
     "cn_timer_stop": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "cn_profile_report": (C.c_int, [_P, C.c_char_p, C.c_int64]),
+    "cn_dot_noalloc": (C.c_int, [_P, _P, C.c_int64, _P, _P]),
     "cn_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "cn_set_option": (C.c_int, [_P, C.c_char_p, C.c_int64]),
 }

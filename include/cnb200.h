@@ -136,6 +136,23 @@ int cn_timer_stop(cn_context* ctx, float* milliseconds);
  * (it has no timers at all). */
 int cn_profile_report(cn_context* ctx, char* buf, int64_t cap);
 
+/* Dot product that allocates nothing: result[0] = sum_i a[i] * b[i] for two float64 device
+ * arrays of n elements, result a device pointer, launched on `stream` (a cudaStream_t, NULL
+ * for the default stream) of the current device.  No counterpart in the reference.
+ * For callers that cannot allocate device memory -- inside another runtime's callback, after
+ * the application has claimed all memory as its own arena, on an out-of-memory error path,
+ * or where touching the allocator is ruled out for latency or determinism.  The per-block
+ * partial sums of the deterministic two-pass reduction live in a fixed 256 KiB array inside
+ * the library image instead of an allocated buffer; neither this call nor anything it calls
+ * allocates or frees.  Limit: n <= CN_NOALLOC_MAX_ELEMS (one partial per 8192 elements),
+ * otherwise CN_STATUS_LIMIT and nothing is launched.  The first call on a device resolves the
+ * array's device address: make it outside stream capture.  All calls on a device share the
+ * array (the ticket counter is cleared on the stream before each launch); calls whose
+ * kernels may overlap on the GPU race on it and must be ordered by the caller.  Needs no
+ * context. */
+#define CN_NOALLOC_MAX_ELEMS 268435456LL
+int cn_dot_noalloc(const double* a, const double* b, int64_t n, double* result, void* stream);
+
 /* Counters since context creation. */
 typedef struct cn_stats {
     int64_t kernel_launches;   /* kernels of this library launched */
@@ -152,8 +169,8 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
 
 /* Options: "halo" depth (rows per side, default 1; set before creating arrays),
  * "fuse_reductions" 0/1, "tile_tx" / "tile_rows" (shape of generated kernels: threads along
- * the last dimension, rows per thread), "staged" 0/1 (TMA / shared-memory staging of stencil
- * tiles; process-wide), "staged_tile_tx" / "staged_tile_rows", "profile" 0/1. */
+ * the last dimension, rows per thread), "staged" 0/1/2 (TMA / shared-memory staging of stencil
+ * tiles: never / 3-D groups only (default) / 2-D groups too; process-wide), "staged_tile_tx" / "staged_tile_rows", "profile" 0/1. */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus
