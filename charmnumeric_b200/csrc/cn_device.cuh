@@ -53,6 +53,7 @@ struct
 
 __device__ const double cn_exp_hi[64] = {CN_EXP_TABLE_HI};
 __device__ const double cn_exp_lo[64] = {CN_EXP_TABLE_LO};
+__device__ const double2 cn_exp_pair[64] = {CN_EXP_TABLE_PAIRS};  // {hi, lo}: one 128-bit load
 
 // 2^m * v for v in [1, 4): one exponent-field add when the result stays normal, two
 // exact power-of-two multiplies otherwise (gradual underflow / overflow to inf).
@@ -70,7 +71,7 @@ __device__ __forceinline__ double cn_scale2(double v, int m) {
 // exp(x) = 2^m * 2^(j/64) * e^r with |r| <= ln2/128; degree-5 polynomial for e^r - 1.
 // Every step is an explicitly rounded IEEE operation (fma / mul / add), so the host
 // restatement that performs the same steps with C fma() gives identical bits.
-__device__ __forceinline__ double cn_exp(double x) {
+static __device__ __noinline__ double cn_exp_slow(double x) {
     if (!(x == x)) return x;
     if (x > 709.782712893384) return __longlong_as_double(0x7ff0000000000000LL);
     if (x < -745.1332191019412) return 0.0;
@@ -89,6 +90,26 @@ __device__ __forceinline__ double cn_exp(double x) {
     double hi = cn_exp_hi[j], lo = cn_exp_lo[j];
     double v = hi + __fma_rn(hi, q, lo);
     return cn_scale2(v, m);
+}
+
+// Same steps as cn_exp_slow, minus everything that cannot happen for |x| < 708: no NaN /
+// overflow / underflow tests (one integer compare on the high word sends those to the slow
+// routine), the scale is a plain add to the exponent field, hi and lo come in one load.
+__device__ __forceinline__ double cn_exp(double x) {
+    if ((__double2hiint(x) & 0x7fffffff) >= 0x40862000) return cn_exp_slow(x);
+    const double shift = 6755399441055744.0;
+    double t = __fma_rn(x, CN_INV_LN2_64, shift);
+    int ki = __double2loint(t);
+    double kd = t - shift;
+    double r = __fma_rn(-kd, CN_LN2_64_HI, x);
+    r = __fma_rn(-kd, CN_LN2_64_LO, r);
+    double p = __fma_rn(r, 0x1.1111111111111p-7, 0x1.5555555555555p-5);
+    p = __fma_rn(p, r, 0x1.5555555555555p-3);
+    p = __fma_rn(p, r, 0.5);
+    double q = __fma_rn(p, r * r, r);
+    const double2 tab = cn_exp_pair[ki & 63];
+    double v = tab.x + __fma_rn(tab.x, q, tab.y);
+    return __hiloint2double(__double2hiint(v) + ((ki >> 6) << 20), __double2loint(v));
 }
 
 // expm1(y) for 0 <= y <= 1.1 with the same reduction; (hi*2^m - 1) is exact there.

@@ -71,6 +71,7 @@ struct Gen {
     }
 
     bool staged_mode = false;  // stencil array comes from the shared-memory ring
+    bool fast_loads = false;   // inside a row-interior tile: every load is unconditional
     // slot of each distinct input array, in order of first use (SHIFTED class)
     std::vector<int> in_names;
     int in_slot(int name) {
@@ -146,6 +147,7 @@ struct Gen {
         return s.str();
     }
     std::string guard_any(int domain) const {
+        if (fast_loads) return "(true)";
         std::string base = (domain == DOM_REGION && g.two_domains) ? "act" : "bx";
         if (g.vec == 1) return "(" + base + "0)";
         return "(" + base + "0 | " + base + "1)";
@@ -367,9 +369,15 @@ struct Gen {
         // CN_R rows up front and reuse rows shared by consecutive stencil rows.
         auto emit_guards = [&](bool fast) {
             if (fast) {
-                for (int e = 0; e < V; ++e) o << "      const bool bx" << e << " = true;\n";
+                // rows (and planes) of the tile are all inside the region: only the position
+                // along the last dimension still decides what an element does
+                for (int e = 0; e < V; ++e)
+                    o << "      const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
+                      << " < xhi);\n";
                 if (g.two_domains)
-                    for (int e = 0; e < V; ++e) o << "      const bool act" << e << " = true;\n";
+                    for (int e = 0; e < V; ++e)
+                        o << "      const bool act" << e << " = (x + " << e << " >= rxlo) & (x + "
+                          << e << " < rxhi);\n";
                 return;
             }
             for (int e = 0; e < V; ++e)
@@ -401,8 +409,11 @@ struct Gen {
                 else o << "      const long long p = z * s0 + y * s1 + x;\n";
             }
             emit_guards(fast);
-            o << "      if " << guard_any(DOM_BOX) << " {\n";
+            if (fast) o << "      if (x < xhi) {\n";
+            else o << "      if " << guard_any(DOM_BOX) << " {\n";
+            fast_loads = fast;
             shifted_body("        ");
+            fast_loads = false;
             o << "      }\n";
             o << "    }\n";
         };
@@ -431,9 +442,8 @@ struct Gen {
             o << "    const long long ybase = ty0 + ly * CN_R;\n";
             const std::string dom = g.two_domains ? "a.rlo" : "a.lo";
             const std::string domh = g.two_domains ? "a.rhi" : "a.hi";
-            o << "    const bool interior = (tx0 >= " << ilo << ") & (tx0 + CN_TX * " << V << " <= " << ihi
-              << ") & (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + (CN_BLOCK / CN_TX) * CN_R <= "
-              << domh << "[" << (N - 2) << "])";
+            o << "    const bool interior = (ty0 >= " << dom << "[" << (N - 2)
+              << "]) & (ty0 + (CN_BLOCK / CN_TX) * CN_R <= " << domh << "[" << (N - 2) << "])";
             if (N == 3 && g.two_domains) o << " & (z >= a.rlo[0]) & (z < a.rhi[0])";
             o << ";\n";
         }
@@ -507,9 +517,13 @@ struct Gen {
 
         auto emit_guards = [&](bool fast) {
             if (fast) {
-                for (int e = 0; e < V; ++e) o << "        const bool bx" << e << " = true;\n";
+                for (int e = 0; e < V; ++e)
+                    o << "        const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
+                      << " < xhi);\n";
                 if (g.two_domains)
-                    for (int e = 0; e < V; ++e) o << "        const bool act" << e << " = true;\n";
+                    for (int e = 0; e < V; ++e)
+                        o << "        const bool act" << e << " = (x + " << e << " >= rxlo) & (x + "
+                          << e << " < rxhi);\n";
                 return;
             }
             for (int e = 0; e < V; ++e)
@@ -536,15 +550,17 @@ struct Gen {
             else o << "        const long long p = z * s0 + y * s1 + x;\n";
             o << "        const int sq = (ly * CN_R + r + CN_HY) * CN_SW + lx * 2;\n";
             emit_guards(fast);
-            o << "        if " << guard_any(DOM_BOX) << " {\n";
+            if (fast) o << "        if (x < xhi) {\n";
+            else o << "        if " << guard_any(DOM_BOX) << " {\n";
+            fast_loads = fast;
             shifted_body("          ");
+            fast_loads = false;
             o << "        }\n";
             o << "      }\n";
         };
         auto emit_interior = [&]() {
-            o << "      const bool interior = (tx0 >= " << ilo << ") & (tx0 + CN_TXE <= " << ihi
-              << ") & (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + CN_TYT <= " << domh << "["
-              << (N - 2) << "])";
+            o << "      const bool interior = (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + CN_TYT <= "
+              << domh << "[" << (N - 2) << "])";
             if (N == 3 && g.two_domains) o << " & (z >= a.rlo[0]) & (z < a.rhi[0])";
             o << ";\n";
             o << "      if (interior) {\n";
