@@ -236,6 +236,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
     } else if (k == "staged_tile_rows") {
         if (value < 1 || value > 16) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_staged_tile(-1, (int)value);
+    } else if (k == "debug_drop_copies") {
+        ctx->impl.set_debug_drop_copies(value != 0);
     } else if (k == "profile") {
         ctx->impl.set_profile(value != 0);
     } else if (k == "fuse_reductions") {

@@ -204,7 +204,15 @@ __device__ __forceinline__ A cn_sum_partials(const A* partials, A* smem) {
 // Tiles of the stencil array are fetched by the TMA unit into a ring of shared-memory
 // slots; one mbarrier per slot counts the bytes that arrive.  Every wait is bounded: when
 // the bound runs out the kernel records it in the error word and leaves.
+#ifndef CN_WAIT_LIMIT
 #define CN_WAIT_LIMIT 20000000u
+#endif
+// Test hook: with CN_DEBUG_DROP_COPIES the elected thread issues no tile copy at all, so every
+// consumer's bounded wait runs out.  Nothing is left in flight and nothing faults; it only
+// exists to exercise the error path (error word -> status code at the next synchronise).
+#ifndef CN_DEBUG_DROP_COPIES
+#define CN_DEBUG_DROP_COPIES 0
+#endif
 
 __device__ __forceinline__ unsigned int cn_smem_addr(const void* p) {
     return (unsigned int)__cvta_generic_to_shared(p);

@@ -578,6 +578,7 @@ struct Gen {
             o << "    const long long fx = xbase + (long long)(tile % ntx) * CN_TXE - 2 + a.tm_off[1];\n";
             o << "    const long long fy = a.lo[0] + (long long)(tile / ntx) * CN_TYT - CN_HY + a.tm_off[0];\n";
             o << "    const unsigned int s = k % CN_NS;\n";
+            o << "    if (CN_DEBUG_DROP_COPIES) return;\n";
             o << "    cn_mbar_expect_tx(&full[s], (unsigned int)(CN_BOX * sizeof(T)));\n";
             o << "    cn_tma_load_2d(ring + (size_t)s * CN_SLOT, a.tmap, (int)fx, (int)fy, &full[s]);\n";
             o << "  };\n";
@@ -618,6 +619,7 @@ struct Gen {
             o << "    const long long ybase = ty0 + ly * CN_R;\n";
             o << "    auto issue = [&](unsigned int i) {\n";
             o << "      const unsigned int s = (gs + i) % CN_NS;\n";
+            o << "      if (CN_DEBUG_DROP_COPIES) return;\n";
             o << "      cn_mbar_expect_tx(&full[s], (unsigned int)(CN_BOX * sizeof(T)));\n";
             o << "      cn_tma_load_3d(ring + (size_t)s * CN_SLOT, a.tmap, (int)(tx0 - 2 + a.tm_off[2]), "
                  "(int)(ty0 - CN_HY + a.tm_off[1]), (int)(zs - CN_HZ + (long long)i + a.tm_off[0]), &full[s]);\n";

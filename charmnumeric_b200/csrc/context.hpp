@@ -131,6 +131,7 @@ public:
         if (tx > 0) staged_tile_.tx = tx;
         if (r > 0) staged_tile_.r = r;
     }
+    void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; }
 
 private:
     int fail(int code, const std::string& msg);
@@ -174,6 +175,7 @@ private:
     int device_, rank_, nranks_;
     int halo_ = 1;
     bool fuse_reductions_ = true;
+    bool debug_drop_copies_ = false;  // test hook: staged kernels issue no tile copies
     bool initialised_ = false;
     int sm_count_ = 148;
     cudaStream_t stream_ = nullptr;

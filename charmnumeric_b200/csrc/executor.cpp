@@ -36,8 +36,9 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         tile.s0 = g.ndims == 2 ? g.array_shape[1] : g.array_shape[1] * g.array_shape[2];
         tile.s1 = g.ndims == 3 ? g.array_shape[2] : 0;
     }
+    tile.drop_copies = g.staged && debug_drop_copies_;
     std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
-                      std::to_string(tile.s0) + "," + std::to_string(tile.s1);
+                      std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "");
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -416,7 +417,17 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         a.error = error_word_;
     }
     a.ntiles = ntiles;
-    int grid = (int)std::min<int64_t>(std::max<int64_t>(ntiles, 1), (int64_t)sm_count_ * k->blocks_per_sm);
+    // Grid: persistent blocks (one wave) when there are many tiles per block; with only a few
+    // tiles per resident block a static split leaves a long tail, so small problems get one
+    // block per tile and the hardware scheduler balances them.  Kernels with a fused
+    // reduction stay within the partial-sum scratch; staged 3-D kernels always march.
+    const int64_t resident = (int64_t)sm_count_ * k->blocks_per_sm;
+    int64_t grid64 = std::min<int64_t>(std::max<int64_t>(ntiles, 1), resident);
+    if (ntiles > resident && ntiles <= 16 * resident && !(g.staged && nd == 3)) {
+        const int64_t cap = g.reds.empty() ? (int64_t)1 << 20 : (int64_t)max_grid_;
+        if (ntiles <= cap) grid64 = ntiles;
+    }
+    int grid = (int)grid64;
 
     std::vector<Array*> results;
     if ((rc = bind_reductions(g, &a, grid, &results))) return rc;

@@ -19,6 +19,8 @@ struct TileConfig {
     // element strides of the arrays a stencil kernel is specialised for (0: read at run time);
     // as compile-time constants they turn every stencil arm into an immediate address offset
     long long s0 = 0, s1 = 0;
+    // test hook of the staged kernels: issue no tile copies and give up waiting quickly
+    bool drop_copies = false;
 };
 
 // Compile CUDA source to a cubin image for sm_100a.  Works without a GPU.

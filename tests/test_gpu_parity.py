@@ -372,3 +372,41 @@ def test_error_codes(interface):
     # the context stays usable after errors
     a = cnp.ones((16,))
     assert np.array_equal((a + a).get(interface), np.full(16, 2.0))
+
+
+def test_bounded_device_wait_reports_status(interface):
+    """Failure path of the staged stencil kernels, without faulting or hanging anything: with
+    the test hook on, the elected thread issues no tile copy, every consumer's bounded wait runs
+    out, the kernel leaves, and the next synchronise reports it as a status code.  The context
+    stays usable."""
+    from charmnumeric_b200._lib import CnError
+    ctx = interface.context
+    prog = _jacobi2d_program(64, 256, 1)
+    try:
+        ctx.set_option("staged", 2)
+        ctx.set_option("debug_drop_copies", 1)
+        cnp.reset_frontend_state()
+        outs = prog()
+        with pytest.raises(CnError) as e:
+            outs["u"].get(interface)
+        assert e.value.status == 8 and "gave up waiting" in e.value.message
+    finally:
+        ctx.set_option("debug_drop_copies", 0)
+        ctx.set_option("staged", 1)
+    gpu, cpu = run_both(interface, prog)
+    assert_bit_exact(gpu, cpu)
+
+
+def test_rank_marked_failed_stops_collective_work():
+    """Host-side failure notice: once a rank is marked failed, DAG submission returns
+    CN_STATUS_RANK_FAILED instead of enqueuing work that would wait for that rank."""
+    from charmnumeric_b200._lib import CnError
+    ctx = cnp.Context(device=0)
+    try:
+        ctx.run([])
+        ctx.mark_rank_failed(0)
+        with pytest.raises(CnError) as e:
+            ctx.run([])
+        assert e.value.status == 14
+    finally:
+        ctx.close()
