@@ -44,6 +44,24 @@ def measured_peak():
         return PEAKS_FALLBACK_GBS, "fallback"
 
 
+def dram_traffic(kernel, wl):
+    """DRAM bytes per launch of the dominant kernel, from the committed ncu capture of that
+    kernel (profiles/dram_traffic.json: measured dram read+write bytes per algorithmic byte on a
+    reduced-size case; traffic of these streaming kernels grows in proportion to the points
+    processed).  None when no capture covers the kernel."""
+    try:
+        table = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
+    except Exception:
+        return None
+    label = kernel["kernel"]
+    for entry in table.get("kernels", []):
+        if entry["match"] in label:
+            launches = max(1, kernel["launches"])
+            algorithmic = kernel["gbs"] * 1e9 * kernel["ms_per_launch"] * 1e-3
+            return entry["dram_bytes_per_algorithmic_byte"] * algorithmic
+    return None
+
+
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -58,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.device)],
+                 "-lms", "100", "-i", str(self.device)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -282,7 +300,6 @@ def run_gpu(args, rank, world, local_rank):
         last = wl.read_result()
     ctx.synchronize()
     e2e_s = max_over_ranks(dist, time.perf_counter() - t0)
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- per-kernel profile over K more steps (event pairs around every launch) ----
     ctx.profile(True)
@@ -291,6 +308,8 @@ def run_gpu(args, rank, world, local_rank):
         step_index += 1
     prof = ctx.profile_report()
     ctx.profile(False)
+    # the sampler ran through the device-timed, end-to-end and profiled passes (same workload)
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -305,22 +324,27 @@ def run_gpu(args, rank, world, local_rank):
                                 "share": r["ms"] / total_ms, "gbs": gbs})
             top = kernels[0]
             roofline = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
-                        "frac": top["gbs"] / peak, "traffic": None, "kernel": top["kernel"],
+                        "frac": top["gbs"] / peak, "traffic": dram_traffic(top, wl), "kernel": top["kernel"],
                         "peak_kind": peak_kind, "nominal_frac": top["gbs"] / 8000.0}
-        value = K / (ms * 1e-3)
+        # weak scaling: every GPU iterates its own slab of the (N times larger) global grid, so the
+        # whole-job figure is GPUs x iterations/s; strong scaling: one fixed problem, steps/s
+        agg = world if wl.scaling == "weak" else 1
+        value = agg * K / (ms * 1e-3)
         step_gbs = wl.bytes_per_step / world / (ms / K * 1e-3) / 1e9
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": wl.scaling,
             "vs_baseline": None, "dtype": "f64", "data": "synthetic",
             "config": {"workload": wl.description, "l2": "working set far larger than L2; no flush",
-                       "parallelism": f"slab{world}", "scale": args.scale},
+                       "parallelism": f"slab{world}", "scale": args.scale,
+                       "aggregate": ("value = GPUs x iterations/s of the per-GPU slab" if agg > 1
+                                     else "value = steps/s of the whole problem")},
             "roofline": roofline,
             "step_hbm": {"algorithmic_bytes_per_step_per_gpu": wl.bytes_per_step / world,
                          "gbs_per_gpu": step_gbs, "frac_of_" + peak_kind: step_gbs / peak,
                          "frac_of_nominal_8000": step_gbs / 8000.0},
             "kernels": kernels,
-            "e2e": {"value": K / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": blob_bytes,
+            "e2e": {"value": agg * K / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": blob_bytes,
                     "d2h_bytes_per_step": 8, "last_result": last},
             "gpu_launches": int(launches),
             "clocks": clocks,

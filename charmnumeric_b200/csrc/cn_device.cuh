@@ -205,7 +205,7 @@ __device__ __forceinline__ A cn_sum_partials(const A* partials, A* smem) {
 // slots; one mbarrier per slot counts the bytes that arrive.  Every wait is bounded: when
 // the bound runs out the kernel records it in the error word and leaves.
 #ifndef CN_WAIT_LIMIT
-#define CN_WAIT_LIMIT 20000000u
+#define CN_WAIT_LIMIT 2000000u
 #endif
 // Test hook: with CN_DEBUG_DROP_COPIES the elected thread issues no tile copy at all, so every
 // consumer's bounded wait runs out.  Nothing is left in flight and nothing faults; it only
@@ -232,7 +232,10 @@ __device__ __forceinline__ void cn_mbar_expect_tx(unsigned long long* bar, unsig
                  : "memory");
 }
 
-// true when the phase with the given parity has completed; false when the bound ran out
+// true when the phase with the given parity has completed; false when the bound ran out.
+// Each poll may suspend the thread for at most about CN_WAIT_HINT_NS (the hint operand of
+// try_wait), so the whole wait is bounded by roughly CN_WAIT_LIMIT * CN_WAIT_HINT_NS.
+#define CN_WAIT_HINT_NS 2000u
 __device__ __forceinline__ bool cn_mbar_wait(unsigned long long* bar, unsigned int parity) {
     const unsigned int addr = cn_smem_addr(bar);
     for (unsigned int i = 0; i < CN_WAIT_LIMIT; ++i) {
@@ -240,11 +243,11 @@ __device__ __forceinline__ bool cn_mbar_wait(unsigned long long* bar, unsigned i
         asm volatile(
             "{\n"
             ".reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
             "selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(CN_WAIT_HINT_NS)
             : "memory");
         if (done) return true;
     }

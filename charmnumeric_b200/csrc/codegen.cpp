@@ -72,6 +72,7 @@ struct Gen {
 
     bool staged_mode = false;  // stencil array comes from the shared-memory ring
     bool fast_loads = false;   // inside a row-interior tile: every load is unconditional
+    bool carry_mode = false;   // staged 3-D march: the thread's own column is carried in registers
     // slot of each distinct input array, in order of first use (SHIFTED class)
     std::vector<int> in_names;
     int in_slot(int name) {
@@ -223,10 +224,19 @@ struct Gen {
                 o << ind << "if " << guard_any(row.domain) << " {\n";
             }
             std::set<int64_t> done;
+            if (smem && carry_mode && N == 3 && row.d1 == 0) {
+                // the thread's own two columns of planes z-1, z, z+1 sit in registers
+                for (int64_t c = 0; c < 2; ++c)
+                    if (row.cols.count(c)) {
+                        o << ind << "  " << colname((int)r, c) << " = cz" << (row.d0 + g.hz) << "[r][" << c
+                          << "];\n";
+                        done.insert(c);
+                    }
+            }
             for (int64_t c : row.cols) {
                 if (done.count(c)) continue;
                 bool even = ((c % 2) + 2) % 2 == 0;
-                if (V == 2 && even && row.cols.count(c + 1)) {
+                if (V == 2 && even && row.cols.count(c + 1) && !done.count(c + 1)) {
                     o << ind << "  { const T2 q = *(const T2*)(" << base.str() << " + (" << c
                       << "LL)); " << colname((int)r, c) << " = q.x; " << colname((int)r, c + 1)
                       << " = q.y; }\n";
@@ -272,7 +282,10 @@ struct Gen {
                 ptr.str("");
                 ptr << "sp" << g.hz << " + sq + (0) * CN_SW + 2";
             }
-            if (V == 2) {
+            if (carry_mode && staged_mode && g.outs[m].name == g.stage_array) {
+                o << ind << "  old" << m << "_0 = cz" << g.hz << "[r][0]; old" << m << "_1 = cz" << g.hz
+                  << "[r][1];\n";
+            } else if (V == 2) {
                 o << ind << "  const T2 q = *(const T2*)(" << ptr.str() << " + (0LL));\n";
                 o << ind << "  old" << m << "_0 = q.x; old" << m << "_1 = q.y;\n";
             } else {
@@ -488,7 +501,8 @@ struct Gen {
         red_decl();
         const int L = N - 1;
         const int NS = N == 3 ? 2 * g.hz + 3 : 3;
-        o << "  enum { CN_HY = " << g.hy << ", CN_HZ = " << g.hz << ", CN_NS = " << NS
+        carry_mode = N == 3 && g.hz == 1;
+        o << "  enum { CN_HY = " << g.hy << ", CN_HZ = " << g.hz << ", CN_NS = CN_NS_OVERRIDE ? CN_NS_OVERRIDE : " << NS
           << ", CN_TXE = CN_TX * 2, CN_SW = CN_TXE + 4, CN_TYT = (CN_BLOCK / CN_TX) * CN_R, "
              "CN_SH = CN_TYT + 2 * CN_HY, CN_BOX = CN_SH * CN_SW, CN_SLOT = (CN_BOX + 15) / 16 * 16 };\n";
         o << "  extern __shared__ __align__(128) unsigned char cn_dyn[];\n";
@@ -627,6 +641,8 @@ struct Gen {
             o << "    if (threadIdx.x == 0)\n";
             o << "      for (unsigned int i = 0; i < total && i < CN_NS; ++i) issue(i);\n";
             o << "    unsigned int waited = 0;\n";
+            if (carry_mode)
+                o << "    T cz0[CN_R][2], cz1[CN_R][2], cz2[CN_R][2];  // own columns at z-1, z, z+1\n";
             o << "    for (long long z = zs; z < ze; ++z) {\n";
             o << "      const unsigned int i0 = (unsigned int)(z - zs);\n";
             o << "      while (waited <= i0 + 2 * CN_HZ) {\n";
@@ -638,7 +654,27 @@ struct Gen {
             for (int d = 0; d <= 2 * g.hz; ++d)
                 o << "      const T* const sp" << d << " = ring + (size_t)((gs + i0 + " << d
                   << ") % CN_NS) * CN_SLOT;\n";
+            if (carry_mode) {
+                // one 128-bit shared-memory read per row brings in plane z+1; planes z-1 and z
+                // were read on the two previous steps (on the first step of a chunk, now)
+                o << "#pragma unroll\n";
+                o << "      for (int r = 0; r < CN_R; ++r) {\n";
+                o << "        const int sq = (ly * CN_R + r + CN_HY) * CN_SW + lx * 2;\n";
+                o << "        if (i0 == 0) {\n";
+                o << "          const T2 q0 = *(const T2*)(sp0 + sq + 2); cz0[r][0] = q0.x; cz0[r][1] = q0.y;\n";
+                o << "          const T2 q1 = *(const T2*)(sp1 + sq + 2); cz1[r][0] = q1.x; cz1[r][1] = q1.y;\n";
+                o << "        }\n";
+                o << "        const T2 q2 = *(const T2*)(sp2 + sq + 2); cz2[r][0] = q2.x; cz2[r][1] = q2.y;\n";
+                o << "      }\n";
+            }
             emit_interior();
+            if (carry_mode) {
+                o << "#pragma unroll\n";
+                o << "      for (int r = 0; r < CN_R; ++r) {\n";
+                o << "        cz0[r][0] = cz1[r][0]; cz0[r][1] = cz1[r][1];\n";
+                o << "        cz1[r][0] = cz2[r][0]; cz1[r][1] = cz2[r][1];\n";
+                o << "      }\n";
+            }
             o << "      __syncthreads();\n";
             o << "      if (threadIdx.x == 0 && i0 + CN_NS < total) issue(i0 + CN_NS);\n";
             o << "    }\n";

@@ -27,11 +27,16 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
     staged_tile_.tx = 64;
     staged_tile_.r = 4;
+    if (const char* n = getenv("CN_STAGED_NS")) {
+        int v = atoi(n);
+        if (v >= 4 && v <= 12) staged_ns_ = v;
+    }
     if (const char* t = getenv("CN_STAGED_TILE")) {
         int tx = 0, r = 0;
         if (sscanf(t, "%d,%d", &tx, &r) == 2 && tx >= 8 && tx <= 64 && (256 % tx) == 0 && r >= 1 && r <= 16) {
             staged_tile_.tx = tx;
             staged_tile_.r = r;
+            staged_tile_set_ = true;
         }
     }
 }

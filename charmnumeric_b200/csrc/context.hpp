@@ -130,6 +130,7 @@ public:
     void set_staged_tile(int tx, int r) {
         if (tx > 0) staged_tile_.tx = tx;
         if (r > 0) staged_tile_.r = r;
+        staged_tile_set_ = true;
     }
     void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; }
 
@@ -176,6 +177,8 @@ private:
     int halo_ = 1;
     bool fuse_reductions_ = true;
     bool debug_drop_copies_ = false;  // test hook: staged kernels issue no tile copies
+    int staged_ns_ = 0;               // ring depth of staged 3-D kernels (0: default)
+    bool staged_tile_set_ = false;    // the staged tile shape was chosen by the caller
     bool initialised_ = false;
     int sm_count_ = 148;
     cudaStream_t stream_ = nullptr;

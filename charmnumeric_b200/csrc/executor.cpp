@@ -28,6 +28,9 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     if (g.staged) {
         // a staged tile is one TMA box: at most 256 elements per side
         tile = staged_tile_;
+        // measured best: 3-D march 128 columns x 8 rows per plane tile with a 4-deep ring
+        // (small slots, five blocks per SM); 2-D tiles 128 x 16
+        if (g.ndims == 3 && !staged_tile_set_) tile.r = 2;
         if (tile.tx > 64) tile.tx = 64;
         while ((CN_BLOCK / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
     }
@@ -37,8 +40,9 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         tile.s1 = g.ndims == 3 ? g.array_shape[2] : 0;
     }
     tile.drop_copies = g.staged && debug_drop_copies_;
+    if (g.staged && g.ndims == 3) tile.ns = staged_ns_ ? staged_ns_ : (g.hz == 1 ? 4 : 0);
     std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
-                      std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "");
+                      std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns);
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -64,7 +68,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         k.label = lbl;
     }
     if (g.staged) {
-        const int ns = g.ndims == 3 ? 2 * g.hz + 3 : 3;
+        const int ns = tile.ns ? tile.ns : (g.ndims == 3 ? 2 * g.hz + 3 : 3);
         const size_t sw = (size_t)tile.tx * 2 + 4, sh = (size_t)(CN_BLOCK / tile.tx) * tile.r + 2 * g.hy;
         const size_t slot = (sh * sw + 15) / 16 * 16;
         k.smem_bytes = ns * slot * sizeof(double) + ns * sizeof(unsigned long long);

@@ -21,6 +21,7 @@ struct TileConfig {
     long long s0 = 0, s1 = 0;
     // test hook of the staged kernels: issue no tile copies and give up waiting quickly
     bool drop_copies = false;
+    int ns = 0;  // ring depth of the staged kernels (0: the generator's default)
 };
 
 // Compile CUDA source to a cubin image for sm_100a.  Works without a GPU.

@@ -126,10 +126,14 @@ class _State:
 
     def reset(self):
         self.pending = []
-        self.next_name = 1
         self.next_node = 0
-        self.dead = []            # names of materialised arrays whose user object is gone
         self.auto_flush = None    # (interface, threshold)
+        # Names keep counting up across resets and the list of dead arrays is kept: arrays of
+        # an earlier program may still live in a backend context and be released later, and a
+        # late release must never hit a new array that happens to reuse the name.
+        if not hasattr(self, "next_name"):
+            self.next_name = 1
+            self.dead = []        # names of materialised arrays whose user object is gone
 
     def new_name(self):
         n = self.next_name
@@ -141,7 +145,7 @@ _state = _State()
 
 
 def reset_frontend_state():
-    """Forget every pending op and restart naming (the test fixtures call this)."""
+    """Forget every pending op (the test fixtures call this); array names stay unique."""
     _state.reset()
 
 
