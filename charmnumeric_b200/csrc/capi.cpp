@@ -1,4 +1,5 @@
 // extern "C" surface declared in include/cnb200.h.
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -176,6 +177,7 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
         tile.tx = 64;
         tile.r = 4;
     }
+    if (const char* pf = getenv("CN_FLAT_PREFETCH")) tile.prefetch = g.flat && atoi(pf) != 0;
     rc = cn::nvrtc_compile(src, tile, &cubin, &log);
     if (rc) {
         copy_err(log, err, errcap);
@@ -219,6 +221,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->nodes = s.nodes;
     out->bytes_h2d = s.bytes_h2d;
     out->bytes_d2h = s.bytes_d2h;
+    out->plan_hits = s.plan_hits;
     return cn::CN_OK;
 }
 
@@ -238,6 +241,10 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         ctx->impl.set_staged_tile(-1, (int)value);
     } else if (k == "debug_drop_copies") {
         ctx->impl.set_debug_drop_copies(value != 0);
+    } else if (k == "plan_cache") {
+        ctx->impl.set_plan_cache(value != 0);
+    } else if (k == "flat_prefetch") {
+        ctx->impl.set_flat_prefetch(value != 0);
     } else if (k == "profile") {
         ctx->impl.set_profile(value != 0);
     } else if (k == "fuse_reductions") {

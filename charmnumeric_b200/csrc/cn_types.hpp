@@ -141,7 +141,7 @@ struct Dag {
     std::vector<int> deletes;        // arrays released after the DAG has run
 };
 
-// Parse a DAG blob ("CNB1" format, documented in INTEGRATION.md and in wire.cpp).
+// Parse a DAG blob ("CNB1" format; the grammar is written out at the top of wire.cpp).
 // Returns CN_OK or CN_ERR_BAD_BLOB with a message.
 int parse_dag(const char* msg, int64_t size, Dag* out, std::string* err);
 // Parse a single serialized group (the `node` production) for cn_compile_group.

@@ -9,6 +9,7 @@
 // a*b+c is never contracted), and fused reductions end in the deterministic last-block
 // finish of cn_device.cuh.
 #include <map>
+#include <algorithm>
 #include <set>
 #include <sstream>
 
@@ -73,6 +74,7 @@ struct Gen {
     bool staged_mode = false;  // stencil array comes from the shared-memory ring
     bool fast_loads = false;   // inside a row-interior tile: every load is unconditional
     bool carry_mode = false;   // staged 3-D march: the thread's own column is carried in registers
+    bool pref_mode = false;    // flat interior tile: inputs were loaded ahead into cu<row>[r]
     // slot of each distinct input array, in order of first use (SHIFTED class)
     std::vector<int> in_names;
     int in_slot(int name) {
@@ -224,6 +226,12 @@ struct Gen {
                 o << ind << "if " << guard_any(row.domain) << " {\n";
             }
             std::set<int64_t> done;
+            if (pref_mode && !smem) {
+                o << ind << "  " << colname((int)r, 0) << " = cu" << r << "[r].x; " << colname((int)r, 1)
+                  << " = cu" << r << "[r].y;\n";
+                done.insert(0);
+                done.insert(1);
+            }
             if (smem && carry_mode && N == 3 && row.d1 == 0) {
                 // the thread's own two columns of planes z-1, z, z+1 sit in registers
                 for (int64_t c = 0; c < 2; ++c)
@@ -381,6 +389,13 @@ struct Gen {
         // guard: every load is unconditional, so the compiler can issue the loads of all
         // CN_R rows up front and reuse rows shared by consecutive stencil rows.
         auto emit_guards = [&](bool fast) {
+            if (fast && N == 1) {
+                // a flat interior tile lies inside the region from end to end
+                for (int e = 0; e < V; ++e) o << "      const bool bx" << e << " = true;\n";
+                if (g.two_domains)
+                    for (int e = 0; e < V; ++e) o << "      const bool act" << e << " = true;\n";
+                return;
+            }
             if (fast) {
                 // rows (and planes) of the tile are all inside the region: only the position
                 // along the last dimension still decides what an element does
@@ -422,7 +437,8 @@ struct Gen {
                 else o << "      const long long p = z * s0 + y * s1 + x;\n";
             }
             emit_guards(fast);
-            if (fast) o << "      if (x < xhi) {\n";
+            if (fast && N == 1) o << "      {\n";
+            else if (fast) o << "      if (x < xhi) {\n";
             else o << "      if " << guard_any(DOM_BOX) << " {\n";
             fast_loads = fast;
             shifted_body("        ");
@@ -432,6 +448,20 @@ struct Gen {
         };
         const char* ilo = g.two_domains ? "rxlo" : "xlo";
         const char* ihi = g.two_domains ? "rxhi" : "xhi";
+        // distinct (array, domain) pairs of a flat group, in the order shifted_body numbers them
+        std::vector<std::pair<int, int>> flat_rows;
+        if (N == 1)
+            for (auto& l : g.leaves) {
+                std::pair<int, int> key(l.name, l.domain);
+                if (std::find(flat_rows.begin(), flat_rows.end(), key) == flat_rows.end())
+                    flat_rows.push_back(key);
+            }
+        const bool prefetch = g.flat && V == 2 && !flat_rows.empty();
+        if (prefetch) {
+            o << "#if CN_PREFETCH\n  bool have = false;\n";
+            for (size_t k = 0; k < flat_rows.size(); ++k) o << "  T2 nx" << k << "[CN_R] = {};\n";
+            o << "#endif\n";
+        }
         if (N == 1) {
             o << "  for (unsigned int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
             o << "    const long long t0 = xbase + (long long)tile * (CN_R * CN_BLOCK * " << V << ");\n";
@@ -461,8 +491,42 @@ struct Gen {
             o << ";\n";
         }
         o << "    if (interior) {\n";
-        emit_rows(true);
+        if (prefetch) {
+            // Software pipeline over the block's list of tiles: the inputs of the next
+            // interior tile are requested before this tile's arithmetic starts, so that long
+            // dependent chains (exp, sqrt, division) do not leave the memory system idle.
+            const std::string tstep = "(CN_R * CN_BLOCK * 2)";
+            auto load_all = [&](const char* dst, const char* base) {
+                o << "#pragma unroll\n      for (int r = 0; r < CN_R; ++r) {\n";
+                for (size_t k = 0; k < flat_rows.size(); ++k)
+                    o << "        " << dst << k << "[r] = *(const T2*)(in" << in_slot(flat_rows[k].first)
+                      << " + " << base << " + (long long)r * (CN_BLOCK * 2) + threadIdx.x * 2);\n";
+                o << "      }\n";
+            };
+            o << "#if CN_PREFETCH\n";
+            for (size_t k = 0; k < flat_rows.size(); ++k) o << "      T2 cu" << k << "[CN_R];\n";
+            o << "      if (have) {\n#pragma unroll\n        for (int r = 0; r < CN_R; ++r) {";
+            for (size_t k = 0; k < flat_rows.size(); ++k) o << " cu" << k << "[r] = nx" << k << "[r];";
+            o << " }\n      } else {\n";
+            load_all("cu", "t0");
+            o << "      }\n";
+            o << "      const unsigned int ntile = tile + gridDim.x;\n";
+            o << "      const long long n0 = xbase + (long long)ntile * " << tstep << ";\n";
+            o << "      have = (ntile < ntiles) & (n0 + " << tstep << " <= " << ihi << ");\n";
+            o << "      if (have) {\n";
+            load_all("nx", "n0");
+            o << "      }\n";
+            pref_mode = true;
+            emit_rows(true);
+            pref_mode = false;
+            o << "#else\n";
+            emit_rows(true);
+            o << "#endif\n";
+        } else {
+            emit_rows(true);
+        }
         o << "    } else {\n";
+        if (prefetch) o << "#if CN_PREFETCH\n      have = false;\n#endif\n";
         emit_rows(false);
         o << "    }\n";
         o << "  }\n";

@@ -60,6 +60,26 @@ struct CompiledGroup {
     std::string log;
 };
 
+// A DAG blob that has run once keeps what was derived from its bytes alone: the parsed
+// nodes, which reductions were folded into which group, each group's lowered form and its
+// compiled kernel.  Running the same bytes again skips parsing, lowering and the kernel
+// cache's string keys; everything that depends on the array table (existence, shapes,
+// buffers, halos) is still resolved per run.
+struct PlanStep {
+    size_t index = 0;     // node this step starts at
+    bool group = false;   // a lowered group (g, k valid); otherwise the node runs generically
+    size_t fused = 0;     // REDUCE / SUM nodes folded into the group
+    GroupIR g;
+    CompiledGroup* k = nullptr;
+};
+
+struct Plan {
+    std::string blob;
+    int staged_level = 0;  // process-wide staging level the groups were lowered under
+    Dag dag;
+    std::vector<PlanStep> steps;
+};
+
 struct Stats {
     long long kernel_launches = 0;   // kernels of this library launched (AOT + generated)
     long long group_launches = 0;    // of which generated group kernels
@@ -70,6 +90,7 @@ struct Stats {
     long long fused_reductions = 0;  // REDUCE/SUM nodes folded into a group kernel
     long long nodes = 0;             // DAG nodes executed
     long long bytes_h2d = 0, bytes_d2h = 0;
+    long long plan_hits = 0;         // DAGs served from the plan cache
 };
 
 struct DriverApi {
@@ -121,18 +142,24 @@ public:
     const Stats& stats() const { return stats_; }
     int rank() const { return rank_; }
     int nranks() const { return nranks_; }
-    void set_halo(int h) { halo_ = h; }
-    void set_fuse_reductions(bool f) { fuse_reductions_ = f; }
+    // every option that lowering or kernel selection looks at drops the cached plans
+    void set_halo(int h) { halo_ = h; plans_.clear(); }
+    void set_fuse_reductions(bool f) { fuse_reductions_ = f; plans_.clear(); }
     void set_tile(int tx, int r) {
         if (tx > 0) tile_.tx = tx;
         if (r > 0) tile_.r = r;
+        tile_set_ = true;
+        plans_.clear();
     }
     void set_staged_tile(int tx, int r) {
         if (tx > 0) staged_tile_.tx = tx;
         if (r > 0) staged_tile_.r = r;
         staged_tile_set_ = true;
+        plans_.clear();
     }
-    void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; }
+    void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; plans_.clear(); }
+    void set_flat_prefetch(bool on) { flat_prefetch_ = on; plans_.clear(); }
+    void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
 
 private:
     int fail(int code, const std::string& msg);
@@ -150,8 +177,8 @@ private:
 
     // execution
     int execute_node(const Dag& dag, size_t* index);
-    int execute_group(const DagNode& node, const std::vector<const AstNode*>& fused);
-    int run_group(const GroupIR& g);
+    int run_plan(Plan& plan);
+    int run_lowered(const GroupIR& g, CompiledGroup* k);
     int run_shifted(const GroupIR& g, CompiledGroup* k);
     int run_strided(const GroupIR& g, CompiledGroup* k);
     int run_scalar_only(const GroupIR& g, CompiledGroup* k);
@@ -177,8 +204,13 @@ private:
     int halo_ = 1;
     bool fuse_reductions_ = true;
     bool debug_drop_copies_ = false;  // test hook: staged kernels issue no tile copies
+    bool flat_prefetch_ = false;      // flat kernels load the next tile ahead of the arithmetic
     int staged_ns_ = 0;               // ring depth of staged 3-D kernels (0: default)
     bool staged_tile_set_ = false;    // the staged tile shape was chosen by the caller
+    bool tile_set_ = false;           // the tile shape of the other kernels was chosen by the caller
+    bool plan_cache_ = true;
+    std::unordered_map<uint64_t, Plan> plans_;  // keyed by a hash of the blob bytes
+    Plan* recording_ = nullptr;                 // plan being recorded by the running receive_dag
     bool initialised_ = false;
     int sm_count_ = 148;
     cudaStream_t stream_ = nullptr;

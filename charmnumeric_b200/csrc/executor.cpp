@@ -25,6 +25,14 @@ void array_strides(const Array& a, int64_t* s) {
 
 int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     TileConfig tile = tile_;
+    if (g.flat && !tile_set_) {
+        // exp, tanh, sqrt and division are long dependent chains in double precision: four
+        // rows per thread give the scheduler eight independent elements to interleave
+        int heavy = 0;
+        for (auto& r : g.roots)
+            if (r.opcode == OP_EXP || r.opcode == OP_TANH || r.opcode == OP_SQRT || r.opcode == OP_DIV) ++heavy;
+        if (heavy >= 2) tile.r = 4;
+    }
     if (g.staged) {
         // a staged tile is one TMA box: at most 256 elements per side
         tile = staged_tile_;
@@ -40,9 +48,11 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         tile.s1 = g.ndims == 3 ? g.array_shape[2] : 0;
     }
     tile.drop_copies = g.staged && debug_drop_copies_;
+    tile.prefetch = g.flat && flat_prefetch_;
     if (g.staged && g.ndims == 3) tile.ns = staged_ns_ ? staged_ns_ : (g.hz == 1 ? 4 : 0);
     std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
-                      std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns);
+                      std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
+                      (tile.prefetch ? "|pf" : "");
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -147,17 +157,7 @@ int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block,
     return CN_OK;
 }
 
-int Context::execute_group(const DagNode& node, const std::vector<const AstNode*>& fused) {
-    GroupIR g;
-    int rc = lower_group(node, fused, &g, &err_);
-    if (rc) return rc;
-    return run_group(g);
-}
-
-int Context::run_group(const GroupIR& g) {
-    CompiledGroup* k = nullptr;
-    int rc = get_kernel(g, &k);
-    if (rc) return rc;
+int Context::run_lowered(const GroupIR& g, CompiledGroup* k) {
     switch (g.cls) {
         case GroupIR::SCALAR_ONLY: return run_scalar_only(g, k);
         case GroupIR::SHIFTED: return run_shifted(g, k);

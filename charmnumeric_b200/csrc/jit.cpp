@@ -92,6 +92,7 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
                           "--prec-sqrt=true",           "--std=c++17",     "-lineinfo",
                           d_tx.c_str(),                 d_r.c_str(),       d_s0.c_str(),
                           d_s1.c_str(),                 d_ns.c_str(),
+                          tile.prefetch ? "-DCN_PREFETCH=1" : "-DCN_PREFETCH=0",
                           tile.drop_copies ? "-DCN_DEBUG_DROP_COPIES=1" : "-DCN_DEBUG_DROP_COPIES=0",
                           tile.drop_copies ? "-DCN_WAIT_LIMIT=2000u" : "-DCN_WAIT_LIMIT=2000000u"};
     rc = api->CompileProgram(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);

@@ -22,6 +22,8 @@ struct TileConfig {
     // test hook of the staged kernels: issue no tile copies and give up waiting quickly
     bool drop_copies = false;
     int ns = 0;  // ring depth of the staged kernels (0: the generator's default)
+    // flat kernels: request the next tile's inputs before this tile's arithmetic starts
+    bool prefetch = false;
 };
 
 // Compile CUDA source to a cubin image for sm_100a.  Works without a GPU.

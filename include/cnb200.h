@@ -74,7 +74,7 @@ int cn_mark_rank_failed(cn_context* ctx, int rank);
 
 /* Execute one DAG.  Stands in for the entry method
  * ArrayDAGGroup::receive_dag(int epoch, int size, char msg[size]) (src/backend.ci:15,
- * src/dag_group_receive.cpp:191-575).  `msg` is a CNB1 blob.
+ * src/dag_group_receive.cpp:191-575).  `msg` is a CNB1 blob (grammar: csrc/wire.cpp).
  * Work is enqueued on the context's stream; the call does not wait for the GPU. */
 int cn_receive_dag(cn_context* ctx, int epoch, int64_t size, const char* msg);
 
@@ -164,13 +164,17 @@ typedef struct cn_stats {
     int64_t nodes;             /* DAG nodes executed */
     int64_t bytes_h2d;
     int64_t bytes_d2h;
+    int64_t plan_hits;         /* DAGs whose bytes had run before (parsing and lowering skipped) */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
 /* Options: "halo" depth (rows per side, default 1; set before creating arrays),
  * "fuse_reductions" 0/1, "tile_tx" / "tile_rows" (shape of generated kernels: threads along
  * the last dimension, rows per thread), "staged" 0/1/2 (TMA / shared-memory staging of stencil
- * tiles: never / 3-D groups only (default) / 2-D groups too; process-wide), "staged_tile_tx" / "staged_tile_rows", "profile" 0/1. */
+ * tiles: never / 3-D groups only (default) / 2-D groups too; process-wide), "staged_tile_tx" /
+ * "staged_tile_rows", "profile" 0/1, "plan_cache" 0/1 (default 1: a DAG blob whose bytes,
+ * epoch aside, have run before skips parsing and lowering), "flat_prefetch" 0/1 (default 0:
+ * flat kernels request the next tile's inputs before the arithmetic of the current one). */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus
