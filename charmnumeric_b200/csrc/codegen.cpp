@@ -588,35 +588,33 @@ struct Gen {
         if (N == 3) o << "  const unsigned int nty = (unsigned int)a.nty;\n";
         o << "  const int lx = threadIdx.x % CN_TX, ly = threadIdx.x / CN_TX;\n";
         o << "  bool timed_out = false;\n";
+        if (N == 3 && g.two_domains) o << "  const long long rz0 = a.rlo[0], rz1 = a.rhi[0];\n";
         const char* ilo = g.two_domains ? "rxlo" : "xlo";
         const char* ihi = g.two_domains ? "rxhi" : "xhi";
         const std::string dom = g.two_domains ? "a.rlo" : "a.lo";
         const std::string domh = g.two_domains ? "a.rhi" : "a.hi";
 
+        // In the 3-D march a thread keeps its (x, y) for a whole chunk of planes: what depends
+        // on x alone is worked out once per chunk (pbx*, pact*), not once per plane.
+        const bool hoist = N == 3;
         auto emit_guards = [&](bool fast) {
-            if (fast) {
-                for (int e = 0; e < V; ++e)
-                    o << "        const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
-                      << " < xhi);\n";
-                if (g.two_domains)
-                    for (int e = 0; e < V; ++e)
-                        o << "        const bool act" << e << " = (x + " << e << " >= rxlo) & (x + "
-                          << e << " < rxhi);\n";
-                return;
+            for (int e = 0; e < V; ++e) {
+                if (hoist) o << "        const bool bx" << e << " = pbx" << e << ";\n";
+                else o << "        const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
+                       << " < xhi);\n";
             }
-            for (int e = 0; e < V; ++e)
-                o << "        const bool bx" << e << " = (x + " << e << " >= xlo) & (x + " << e
-                  << " < xhi);\n";
-            if (g.two_domains) {
+            if (!g.two_domains) return;
+            if (!fast) {
                 std::ostringstream rowin;
                 rowin << "true";
                 if (N == 2) rowin << " & (y >= a.rlo[0]) & (y < a.rhi[0])";
-                if (N == 3)
-                    rowin << " & (z >= a.rlo[0]) & (z < a.rhi[0]) & (y >= a.rlo[1]) & (y < a.rhi[1])";
+                if (N == 3) rowin << " & zin & (y >= a.rlo[1]) & (y < a.rhi[1])";
                 o << "        const bool rowin = " << rowin.str() << ";\n";
-                for (int e = 0; e < V; ++e)
-                    o << "        const bool act" << e << " = rowin & (x + " << e
-                      << " >= rxlo) & (x + " << e << " < rxhi);\n";
+            }
+            for (int e = 0; e < V; ++e) {
+                o << "        const bool act" << e << " = " << (fast ? "" : "rowin & ");
+                if (hoist) o << "pact" << e << ";\n";
+                else o << "(x + " << e << " >= rxlo) & (x + " << e << " < rxhi);\n";
             }
         };
         auto emit_rows = [&](bool fast) {
@@ -637,10 +635,13 @@ struct Gen {
             o << "      }\n";
         };
         auto emit_interior = [&]() {
-            o << "      const bool interior = (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + CN_TYT <= "
-              << domh << "[" << (N - 2) << "])";
-            if (N == 3 && g.two_domains) o << " & (z >= a.rlo[0]) & (z < a.rhi[0])";
-            o << ";\n";
+            if (hoist) {
+                if (g.two_domains) o << "      const bool zin = (z >= rz0) & (z < rz1);\n";
+                o << "      const bool interior = yin" << (g.two_domains ? " & zin" : "") << ";\n";
+            } else {
+                o << "      const bool interior = (ty0 >= " << dom << "[" << (N - 2) << "]) & (ty0 + CN_TYT <= "
+                  << domh << "[" << (N - 2) << "]);\n";
+            }
             o << "      if (interior) {\n";
             emit_rows(true);
             o << "      } else {\n";
@@ -705,10 +706,19 @@ struct Gen {
             o << "    if (threadIdx.x == 0)\n";
             o << "      for (unsigned int i = 0; i < total && i < CN_NS; ++i) issue(i);\n";
             o << "    unsigned int waited = 0;\n";
+            for (int e = 0; e < V; ++e)
+                o << "    const bool pbx" << e << " = (x + " << e << " >= xlo) & (x + " << e << " < xhi);\n";
+            if (g.two_domains)
+                for (int e = 0; e < V; ++e)
+                    o << "    const bool pact" << e << " = (x + " << e << " >= rxlo) & (x + " << e << " < rxhi);\n";
+            o << "    const bool yin = (ty0 >= " << dom << "[1]) & (ty0 + CN_TYT <= " << domh << "[1]);\n";
             if (carry_mode)
                 o << "    T cz0[CN_R][2], cz1[CN_R][2], cz2[CN_R][2];  // own columns at z-1, z, z+1\n";
             o << "    for (long long z = zs; z < ze; ++z) {\n";
             o << "      const unsigned int i0 = (unsigned int)(z - zs);\n";
+            // the verdict of the bounded wait is made block-uniform (see the 2-D loop above);
+            // the barrier also keeps the block's warps on the same plane, which measured faster
+            // than letting them drift
             o << "      while (waited <= i0 + 2 * CN_HZ) {\n";
             o << "        const bool ok = cn_mbar_wait(&full[(gs + waited) % CN_NS], ((gs + waited) / CN_NS) & 1u);\n";
             o << "        if (__syncthreads_or(ok ? 0 : 1)) { timed_out = true; break; }\n";

@@ -132,6 +132,7 @@ int Context::init() {
     CN_DRV(GetErrorString, "cuGetErrorString")
     CN_DRV(OccupancyMaxActiveBlocksPerMultiprocessor, "cuOccupancyMaxActiveBlocksPerMultiprocessor")
     CN_DRV(FuncSetAttribute, "cuFuncSetAttribute")
+    CN_DRV(FuncGetAttribute, "cuFuncGetAttribute")
     CN_DRV(TensorMapEncodeTiled, "cuTensorMapEncodeTiled")
     error_word_ = counter_ + 16;  // second cache line of the zeroed 256-byte scratch block
 #undef CN_DRV
@@ -511,9 +512,9 @@ int Context::execute_node(const Dag& dag, size_t* index) {
             case OP_SUM: last = execute_reduce(*r); break;
             case OP_MATMUL: last = execute_matmul(*r); break;
             case OP_RANDU: last = execute_randu(*r); break;
+            case OP_DIAG: last = execute_diag(*r); break;
             case OP_MATMATMUL:
             case OP_TILE:
-            case OP_DIAG:
             case OP_GET_REGION:
                 return fail(CN_ERR_UNSUPPORTED, "opcode " + std::to_string(r->opcode) +
                                                     " is outside this backend's scope");

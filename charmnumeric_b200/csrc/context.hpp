@@ -102,6 +102,7 @@ struct DriverApi {
     CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
     CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
     CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*FuncGetAttribute)(int*, CUfunction_attribute, CUfunction) = nullptr;
     CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -192,6 +193,7 @@ private:
     int execute_reduce(const AstNode& root);
     int execute_matmul(const AstNode& root);
     int execute_randu(const AstNode& root);
+    int execute_diag(const AstNode& root);
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);
     int exchange_halo(Array* a);

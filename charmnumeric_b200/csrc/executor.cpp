@@ -90,6 +90,19 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     int occ = 0;
     if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, CN_BLOCK, k.smem_bytes) == CUDA_SUCCESS && occ > 0)
         k.blocks_per_sm = occ;
+    if (g.staged && g.ndims == 3) {
+        // measured on the 1024^3 sweep: four marching blocks per SM saturate HBM; a fifth only
+        // adds planes in flight and costs 14 %
+        int cap = 4;
+        if (const char* c = getenv("CN_STAGED_BLOCKS")) cap = std::max(1, atoi(c));
+        k.blocks_per_sm = std::min(k.blocks_per_sm, cap);
+    }
+    if (getenv("CN_KERNEL_INFO")) {  // one line per compiled kernel on stderr
+        int regs = 0;
+        drv_.FuncGetAttribute(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, k.func);
+        fprintf(stderr, "[cnb200] %s %s: %d registers, %zu B dynamic smem, %d blocks/SM, tile %dx%d\n",
+                g.entry_name().c_str(), k.label.c_str(), regs, k.smem_bytes, k.blocks_per_sm, tile.tx, tile.r);
+    }
     auto ins = kernels_.emplace(key, std::move(k));
     *out = &ins.first->second;
     return CN_OK;
@@ -400,10 +413,28 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
                 if (g.staged && nd == 3) {
                     // chunks of dimension 0: enough tiles to balance the persistent blocks,
                     // long enough that the 2*hz planes of run-in stay cheap
-                    int64_t want = 4LL * sm_count_ * k->blocks_per_sm;
-                    int64_t nzc = std::max<int64_t>(1, (want + ntx * nty - 1) / (ntx * nty));
-                    int64_t zchunk = std::max<int64_t>(std::min<int64_t>(nz, 32), (nz + nzc - 1) / nzc);
-                    nzc = (nz + zchunk - 1) / zchunk;
+                    // The persistent blocks take chunks round-robin, so the launch lasts as long
+                    // as the block with the most chunks: pick the chunk count whose load balance
+                    // (mean / maximum chunks per block) times run-in efficiency is best.
+                    const int64_t blocks = (int64_t)sm_count_ * k->blocks_per_sm;
+                    const int64_t cols = ntx * nty;
+                    int64_t nzc = 1, zchunk = nz;
+                    double best = -1.0;
+                    for (int64_t c = 1; c <= 64 && c <= nz; ++c) {
+                        const int64_t zc = (nz + c - 1) / c;
+                        if (c > 1 && zc < 16) break;
+                        const int64_t cc = (nz + zc - 1) / zc;
+                        const int64_t tiles = cols * cc;
+                        const double per = (double)tiles / (double)blocks;
+                        const double balance = tiles >= blocks ? per / (double)((tiles + blocks - 1) / blocks)
+                                                               : (double)tiles / (double)blocks;
+                        const double eff = balance * (double)zc / (double)(zc + 2 * g.hz);
+                        if (eff > best + 1e-9) {
+                            best = eff;
+                            nzc = cc;
+                            zchunk = zc;
+                        }
+                    }
                     a.nzc = nzc;
                     a.zchunk = zchunk;
                     ntiles = ntx * nty * nzc;
@@ -723,6 +754,65 @@ int Context::execute_matmul(const AstNode& r) {
     if (rc) return rc;
     stats_.kernel_launches++;
     y->halo_valid = false;
+    return CN_OK;
+}
+
+// DIAG (src/execute_node.cpp:600-750): a vector becomes the k-th diagonal of a zeroed square
+// matrix, or the k-th diagonal of a matrix becomes a vector.  Both are one strided copy.
+// With k = 0 (and rows <= cols for the extraction) the row partition of the matrix and the
+// partition of the vector coincide, so the copy is local on every rank; other cases need the
+// general redistribution and run on one rank only.
+int Context::execute_diag(const AstNode& r) {
+    if (r.operands.size() != 2) return fail(CN_ERR_BAD_BLOB, "DIAG needs (array, k)");
+    const Operand& kop = r.operands[1];
+    if (kop.is_ref || !kop.leaf || !kop.leaf->is_scalar) return fail(CN_ERR_BAD_BLOB, "DIAG offset must be a literal scalar");
+    const int64_t k = (int64_t)kop.leaf->scalar;
+    Array* v = nullptr;
+    Region rv;
+    int rc = operand_array(r.operands[0], &v, &rv);
+    if (rc) return rc;
+    for (int d = 0; d < v->ndims; ++d)
+        if (rv.start[d] != 0 || rv.stop[d] != v->shape[d] || rv.step[d] != 1)
+            return fail(CN_ERR_UNSUPPORTED, "DIAG of a view is not supported; assign the view to an array first");
+    if (r.result_name == v->name) return fail(CN_ERR_HAZARD, "DIAG result aliases its operand");
+    const int64_t roff = k < 0 ? -k : 0, coff = k > 0 ? k : 0;
+    const int vname = v->name, dtype = v->dtype;
+    Array* out = nullptr;
+    StridedView dv, sv;
+    int64_t ext[3] = {1, 1, 0};
+    if (v->ndims == 1) {
+        const int64_t len = v->shape[0], n = len + roff + coff;
+        if (nranks_ > 1 && k != 0) return fail(CN_ERR_UNSUPPORTED, "DIAG with an offset needs a single rank");
+        int64_t shape[2] = {n, n};
+        if ((rc = create_array(r.result_name, 2, shape, dtype, true, &out))) return rc;
+        v = find(vname);
+        ext[2] = v->local_rows();
+        sv.off = 0;
+        sv.str[2] = 1;
+        dv.off = (v->row_begin + roff - out->row_begin) * n + v->row_begin + coff;
+        dv.str[2] = n + 1;
+    } else if (v->ndims == 2) {
+        const int64_t rows = v->shape[0], cols = v->shape[1];
+        const int64_t len = k >= 0 ? std::min(rows, cols - k) : std::min(rows + k, cols);
+        if (len <= 0) return fail(CN_ERR_SHAPE_MISMATCH, "DIAG offset outside the matrix");
+        if (nranks_ > 1 && (k != 0 || rows > cols)) return fail(CN_ERR_UNSUPPORTED, "this DIAG extraction needs a single rank");
+        int64_t shape[1] = {len};
+        if ((rc = create_array(r.result_name, 1, shape, dtype, false, &out))) return rc;
+        v = find(vname);
+        ext[2] = out->local_rows();
+        dv.off = 0;
+        dv.str[2] = 1;
+        sv.off = (out->row_begin + roff - v->row_begin) * cols + out->row_begin + coff;
+        sv.str[2] = cols + 1;
+    } else {
+        return fail(CN_ERR_UNSUPPORTED, "DIAG needs a 1-D or 2-D array");
+    }
+    if (ext[2] > 0) {
+        rc = cuda_fail(launch_copy_region(out->buf.data, dv, v->buf.data, sv, ext, dtype, stream_), "diag");
+        if (rc) return rc;
+        stats_.kernel_launches++;
+    }
+    out->halo_valid = false;
     return CN_OK;
 }
 

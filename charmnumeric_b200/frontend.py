@@ -112,7 +112,7 @@ class _Op:
     __slots__ = ("kind", "opcode", "result", "operands", "region", "payload")
 
     def __init__(self, kind, opcode=None, result=None, operands=(), region=None, payload=None):
-        self.kind = kind          # "ew", "set", "create", "reduce", "sum", "matmul", "randu", "put"
+        self.kind = kind          # "ew", "set", "create", "reduce", "sum", "matmul", "diag", "randu", "put"
         self.opcode = opcode
         self.result = result      # _Info
         self.operands = list(operands)  # (_Info, Region | None) or python scalar
@@ -494,6 +494,27 @@ def _matvec(mat, vec):
     return out
 
 
+def diag(v, k=0):
+    """Diagonal matrix from a vector, or the k-th diagonal of a matrix
+    (charmnumeric/operations.py:125-148)."""
+    v = _whole(asarray(v))
+    k = int(k)
+    if v.ndims == 1:
+        n = v.shape[0] + (k if k >= 0 else -k)
+        shape = (n, n)
+    elif v.ndims == 2:
+        rows, cols = v.shape
+        length = max(0, min(rows, cols - k)) if k >= 0 else max(0, min(rows + k, cols))
+        if length == 0:
+            raise ValueError(f"k={k} is out of range for shape ({rows}, {cols})")
+        shape = (length,)
+    else:
+        raise ValueError(f"diag requires a 1D or 2D array, got {v.ndims}D")
+    out = _new_array(shape, v.dtype)
+    _record(_Op("diag", wire.OP_DIAG, out._info, [v._operand()], payload=k))
+    return out
+
+
 def dot2d(a, b):
     """dot of two same-shaped arrays of any rank (the reference accepts 1-D only)."""
     a, b = _whole(asarray(a)), _whole(asarray(b))
@@ -858,6 +879,10 @@ def _single_node(op):
     elif op.kind in ("reduce", "matmul", "sum"):
         root = wire.Ast(res.name, op.opcode, shape=res.shape, dtype=dt,
                         operands=[(_leaf(i), r) for i, r in op.operands])
+    elif op.kind == "diag":
+        root = wire.Ast(res.name, wire.OP_DIAG, shape=res.shape, dtype=dt,
+                        operands=[(_leaf(i), r) for i, r in op.operands]
+                        + [(wire.scalar(float(op.payload)), None)])
     elif op.kind == "randu":
         root = wire.Ast(res.name, wire.OP_RANDU, shape=res.shape, dtype=dt,
                         operands=[(wire.scalar(v), None) for v in op.operands])

@@ -29,6 +29,7 @@ _LIB = _HERE / "libcn_oracle.so"
 
 OP_COPY, OP_SET_REGION, OP_CREATE, OP_NOOP = -5, -4, -2, -1
 OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MATMUL, OP_TANH, OP_EXP, OP_REDUCE = 0, 1, 2, 3, 4, 5, 6, 8
+OP_DIAG = 10
 OP_SQRT, OP_ABS, OP_SUM, OP_RANDU = 11, 12, 13, 14
 NP_DTYPES = {0: np.dtype("float32"), 1: np.dtype("float64"), 2: np.dtype("int32"),
              3: np.dtype("int64")}
@@ -254,6 +255,11 @@ class Oracle:
                 else:
                     y = (np.asarray(A) @ np.asarray(x)).astype(dtype)
                 self.arrays[r.result_name] = y.astype(dtype)
+            elif op == OP_DIAG:
+                # src/execute_node.cpp:600-750: vector -> diagonal matrix, matrix -> k-th diagonal
+                v = self.arrays[r.operands[0][0].result_name]
+                k = int(r.operands[1][0].scalar)
+                self.arrays[r.result_name] = np.ascontiguousarray(np.diag(v, k)).astype(dtype)
             elif op == OP_RANDU:
                 seed, lo, hi = (o[0].scalar for o in r.operands)
                 self.arrays[r.result_name] = randu(r.shape, int(seed), lo, hi, NP_DTYPES[r.dtype])

@@ -50,7 +50,15 @@ def main():
         x = cnp.random.uniform((128,), seed=22, low=-1.0, high=1.0)
         y = A @ x
         return {"y": y, "n": y @ y}
+
+    def diag():
+        n = 75
+        A = cnp.random.uniform((n, n), seed=31, low=-1.0, high=1.0) + cnp.diag(cnp.full((n,), 2.0 * n))
+        d = cnp.diag(A)
+        x = cnp.random.uniform((n,), seed=32)
+        return {"A": A, "d": d, "x1": x + (1.0 / d) * (cnp.ones((n,)) - A @ x)}
     progs["chain"] = chain
+    progs["diag"] = diag
     progs["matvec"] = matvec
     cnp.reset_frontend_state()
     outs = progs[case]()

@@ -50,6 +50,11 @@ def test_example_cg_dense(cpu_interface):
     G.test_cg_dense_matches_numpy_solve(cpu_interface)
 
 
+@pytest.mark.parametrize("n,k", [(1, 0), (17, 0), (12, 2), (12, -3)])
+def test_diag_through_the_oracle(cpu_interface, n, k):
+    G.test_diag_matches_numpy(cpu_interface, n, k)
+
+
 def _dry(prog):
     cnp.reset_frontend_state()
     outs = prog()

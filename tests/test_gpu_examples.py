@@ -15,6 +15,9 @@ ROOT = Path(__file__).resolve().parent.parent
     ("jacobi3d.py", ["48", "20"]),
     ("cg.py", ["128", "4"]),
     ("matvec.py", ["48"]),
+    ("gauss_seidel.py", ["130", "6"]),
+    ("multigrid2d.py", ["65", "2"]),
+    ("jacobi_iteration.py", ["96", "50"]),
 ])
 def test_example_runs(script, args):
     env_path = str(ROOT)

@@ -17,7 +17,7 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("case", ["jacobi2d", "jacobi2d_small", "jacobi3d", "cg", "chain", "matvec"])
+@pytest.mark.parametrize("case", ["jacobi2d", "jacobi2d_small", "jacobi3d", "cg", "chain", "matvec", "diag"])
 @pytest.mark.parametrize("nranks", [2, 4])
 def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
     if _gpu_count() < nranks:

@@ -218,6 +218,19 @@ def test_matvec_known_answer(interface):
     np.testing.assert_allclose(got, host @ np.ones(N))
 
 
+@pytest.mark.parametrize("n,k", [(1, 0), (48, 0), (131, 0), (40, 3), (40, -5)])
+def test_diag_matches_numpy(interface, n, k):
+    """DIAG both ways (charmnumeric/operations.py:125-148): vector -> matrix, matrix -> vector."""
+    v = np.arange(1.0, n + 1.0)
+    m = np.arange(float((n + 2) * (n + 5))).reshape(n + 2, n + 5)
+    built = cnp.diag(cnp.asarray(v), k).get(interface)
+    assert np.array_equal(built, np.diag(v, k))
+    taken = cnp.diag(cnp.asarray(m), k).get(interface)
+    assert np.array_equal(taken, np.diag(m, k))
+    tall = cnp.diag(cnp.asarray(np.ascontiguousarray(m.T)), k).get(interface)
+    assert np.array_equal(tall, np.diag(m.T, k))
+
+
 def _cg_poisson_program(m, iters):
     def prog():
         b = cnp.zeros((m, m))
