@@ -222,6 +222,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->bytes_h2d = s.bytes_h2d;
     out->bytes_d2h = s.bytes_d2h;
     out->plan_hits = s.plan_hits;
+    out->peer_exchanges = s.peer_exchanges;
     return cn::CN_OK;
 }
 
@@ -241,6 +242,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         ctx->impl.set_staged_tile(-1, (int)value);
     } else if (k == "debug_drop_copies") {
         ctx->impl.set_debug_drop_copies(value != 0);
+    } else if (k == "p2p") {
+        ctx->impl.set_p2p(value != 0);
     } else if (k == "plan_cache") {
         ctx->impl.set_plan_cache(value != 0);
     } else if (k == "flat_prefetch") {

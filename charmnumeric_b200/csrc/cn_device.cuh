@@ -14,6 +14,21 @@
 #define CN_MAX_RED 4
 #define CN_MAX_SOUT 4
 #define CN_BLOCK 256
+#define CN_MAX_PEERS 8
+#define CN_PEER_HALO_SLOT (16u << 20)  // bytes per (bank, direction) halo payload slot
+
+// Mailbox of one rank, in that rank's own device memory; the other ranks of the box write
+// into it over NVLink through peer mappings.  Two banks alternate by epoch parity: a rank
+// can only reach epoch e+2 after every partner has consumed epoch e, so nothing is
+// overwritten while it is still being read.  The halo payload follows the header:
+// slot (bank, dir) starts at byte 4096 + (bank * 2 + dir) * CN_PEER_HALO_SLOT, dir 0 = rows
+// that came from the rank below (rank - 1), dir 1 = from the rank above.
+struct CnPeerBox {
+    unsigned long long red_val[2][CN_MAX_RED][CN_MAX_PEERS];  // [bank][reduction][source rank]
+    unsigned long long red_flag[2][CN_MAX_PEERS];             // epoch of the values of a source rank
+    unsigned long long halo_flag[2][2];                       // [bank][dir]: epoch of the payload
+    unsigned long long pad[(4096 - 8 * (2 * CN_MAX_RED * CN_MAX_PEERS + 2 * CN_MAX_PEERS + 4)) / 8];
+};
 
 // Launch arguments of one fused group kernel.  The same layout is used by the host
 // (it fills the block) and by the generated source (it reads it), so only plain types.
@@ -45,6 +60,10 @@ struct
     long long nzc, zchunk;       // staged 3-D kernels: number and length of the z chunks marched
     long long tm_off[3];         // staged kernels: local coordinate -> descriptor coordinate offset
     unsigned int* error;         // device error word (set when a bounded wait runs out)
+    // fused cross-GPU reduction: every rank's mailbox as mapped on this GPU (peer_n = 0: off)
+    void* peer_box[CN_MAX_PEERS];
+    int peer_rank, peer_n;
+    unsigned long long peer_epoch;
 };
 
 #ifdef __CUDACC__
@@ -198,6 +217,77 @@ __device__ __forceinline__ A cn_sum_partials(const A* partials, A* smem) {
     for (unsigned int i = threadIdx.x; i < gridDim.x; i += blockDim.x)
         v += ((const volatile A*)partials)[i];
     return cn_block_sum(v, smem);  // valid in thread 0
+}
+
+// ---- cross-GPU exchange through peer mailboxes (NVLink loads / stores, no multicast) ----------
+// Every wait on a flag that another GPU writes is bounded: CN_PEER_WAIT_LIMIT polls with a
+// short sleep in between (two to three seconds in all), after which the caller records the
+// failure in the error word and carries on with what it has.
+#ifndef CN_PEER_WAIT_LIMIT
+#define CN_PEER_WAIT_LIMIT 4000000u
+#endif
+
+__device__ __forceinline__ void cn_st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long cn_ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// true once *flag >= epoch; false when the bound ran out
+__device__ __forceinline__ bool cn_peer_wait(const unsigned long long* flag, unsigned long long epoch) {
+    for (unsigned int i = 0; i < CN_PEER_WAIT_LIMIT; ++i) {
+        if (cn_ld_acquire_sys(flag) >= epoch) return true;
+        __nanosleep(40);
+    }
+    return false;
+}
+
+__device__ __forceinline__ unsigned long long cn_bits(double v) { return (unsigned long long)__double_as_longlong(v); }
+__device__ __forceinline__ unsigned long long cn_bits(long long v) { return (unsigned long long)v; }
+__device__ __forceinline__ void cn_unbits(unsigned long long b, double* v) { *v = __longlong_as_double((long long)b); }
+__device__ __forceinline__ void cn_unbits(unsigned long long b, long long* v) { *v = (long long)b; }
+
+// Sum of `n` per-rank totals over all ranks, inside the kernel that produced them.  Called by
+// every thread of the one block that finished the local reduction; `tv` holds this rank's
+// totals in thread 0 on entry and the global totals in thread 0 on return.  Thread r stores
+// the totals into rank r's mailbox and publishes them with a release store of the epoch, then
+// waits for rank r's totals to arrive in this rank's own mailbox; thread 0 adds them in rank
+// order, so every rank computes bit-identical results.
+template <typename A>
+__device__ __forceinline__ void cn_peer_allreduce(const CnGroupArgs& a, A* tv, int n, A* smem) {
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int q = 0; q < n; ++q) smem[q] = tv[q];
+    __syncthreads();
+    const int bank = (int)(a.peer_epoch & 1ULL);
+    CnPeerBox* const me = (CnPeerBox*)a.peer_box[a.peer_rank];
+    bool ok = true;
+    if ((int)threadIdx.x < a.peer_n) {
+        CnPeerBox* const dst = (CnPeerBox*)a.peer_box[threadIdx.x];
+        for (int q = 0; q < n; ++q)
+            *(volatile unsigned long long*)&dst->red_val[bank][q][a.peer_rank] = cn_bits(smem[q]);
+        cn_st_release_sys(&dst->red_flag[bank][a.peer_rank], a.peer_epoch);
+        ok = cn_peer_wait(&me->red_flag[bank][threadIdx.x], a.peer_epoch);
+    }
+    if (__syncthreads_or(ok ? 0 : 1)) {
+        if (threadIdx.x == 0 && a.error) atomicExch(a.error, 2u);
+        return;  // the local totals stay in tv
+    }
+    if (threadIdx.x == 0) {
+        for (int q = 0; q < n; ++q) {
+            A s = (A)0;
+            for (int r = 0; r < a.peer_n; ++r) {
+                A v;
+                cn_unbits(*(volatile unsigned long long*)&me->red_val[bank][q][r], &v);
+                s += v;
+            }
+            tv[q] = s;
+        }
+    }
 }
 
 // ---- TMA / mbarrier helpers (sm_100a) -----------------------------------------------------

@@ -135,11 +135,15 @@ struct Gen {
             o << "    ((ACC*)a.partials)[" << i << " * gridDim.x + blockIdx.x] = bt" << i << ";\n";
         o << "  }\n";
         o << "  if (cn_grid_ticket(a.counter, &cn_flag)) {\n";
-        for (size_t i = 0; i < g.reds.size(); ++i) {
-            o << "    ACC t" << i << " = cn_sum_partials(((const ACC*)a.partials) + " << i
+        o << "    ACC tv[" << g.reds.size() << "];\n";
+        for (size_t i = 0; i < g.reds.size(); ++i)
+            o << "    tv[" << i << "] = cn_sum_partials(((const ACC*)a.partials) + " << i
               << " * gridDim.x, cn_sm);\n";
-            o << "    if (threadIdx.x == 0) *(T*)a.red[" << i << "] = (T)t" << i << ";\n";
-        }
+        // more than one rank: the block that holds the local totals also exchanges them with
+        // the other GPUs' mailboxes and adds them up, so no separate collective follows
+        o << "    if (a.peer_n > 1) cn_peer_allreduce(a, tv, " << g.reds.size() << ", cn_sm);\n";
+        for (size_t i = 0; i < g.reds.size(); ++i)
+            o << "    if (threadIdx.x == 0) *(T*)a.red[" << i << "] = (T)tv[" << i << "];\n";
         o << "    if (threadIdx.x == 0) *a.counter = 0u;\n";
         o << "  }\n";
     }

@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "kernels.hpp"
 
@@ -58,6 +59,13 @@ Context::~Context() {
     if (partials_) cudaFree(partials_);
     if (counter_) cudaFree(counter_);
     if (scratch_) cudaFree(scratch_);
+    if (peer_.ready) {
+        for (int p = 0; p < nranks_; ++p)
+            if (p != rank_ && peer_.box[p]) cudaIpcCloseMemHandle(peer_.box[p]);
+        cudaFree(peer_.ticket);
+        // peer_.mine is not freed here: another rank may still hold a mapping of it, and
+        // freeing exported memory under a live mapping is undefined; it goes with the process
+    }
     if (ev_start_) cudaEventDestroy(ev_start_);
     if (ev_stop_) cudaEventDestroy(ev_stop_);
     cudaStreamSynchronize(stream_);
@@ -271,7 +279,86 @@ int Context::comm_init_id(const char id[128]) {
     if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
     if (nranks_ == 1) return CN_OK;
     cudaSetDevice(device_);
-    return comm_init(&comm_, id, rank_, nranks_, &err_);
+    int rc = comm_init(&comm_, id, rank_, nranks_, &err_);
+    if (rc) return rc;
+    return setup_peer_boxes();
+}
+
+// Allocate this rank's mailbox, hand its IPC handle to every other rank (through the NCCL
+// communicator that already exists) and map theirs.  All ranks then agree, by an allreduce
+// of a success flag, whether the peer path is used; any failure leaves NCCL in charge.
+int Context::setup_peer_boxes() {
+    peer_.ready = false;
+    if (const char* e = getenv("CN_P2P")) p2p_wanted_ = atoi(e) != 0;
+    int ok = (p2p_wanted_ && nranks_ <= CN_MAX_PEERS) ? 1 : 0;
+    const size_t box_bytes = sizeof(CnPeerBox) + 4ull * CN_PEER_HALO_SLOT;
+    cudaIpcMemHandle_t mine_h;
+    memset(&mine_h, 0, sizeof(mine_h));
+    if (ok) {
+        if (cudaMalloc(&peer_.mine, box_bytes) != cudaSuccess || cudaMemset(peer_.mine, 0, sizeof(CnPeerBox)) != cudaSuccess ||
+            cudaIpcGetMemHandle(&mine_h, peer_.mine) != cudaSuccess) {
+            cudaGetLastError();
+            ok = 0;
+        }
+    }
+    // staging area: nranks handles + one flag word
+    const size_t hs = sizeof(cudaIpcMemHandle_t);
+    int rc = ensure_scratch(hs * nranks_ + 256);
+    if (rc) return rc;
+    char* stage = (char*)scratch_;
+    if ((rc = cuda_fail(cudaMemcpyAsync(stage + hs * rank_, &mine_h, hs, cudaMemcpyHostToDevice, stream_), "peer handle"))) return rc;
+    if ((rc = comm_group_start(&err_))) return rc;
+    for (int p = 0; p < nranks_; ++p)
+        if ((rc = comm_broadcast(&comm_, stage + hs * p, stage + hs * p, (int64_t)(hs / 4), DT_I32, p, stream_, &err_))) return rc;
+    if ((rc = comm_group_end(&err_))) return rc;
+    std::vector<cudaIpcMemHandle_t> handles(nranks_);
+    if ((rc = cuda_fail(cudaMemcpyAsync(handles.data(), stage, hs * nranks_, cudaMemcpyDeviceToHost, stream_), "peer handles"))) return rc;
+    if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "peer handles"))) return rc;
+    if (ok) {
+        for (int p = 0; p < nranks_ && ok; ++p) {
+            if (p == rank_) {
+                peer_.box[p] = peer_.mine;
+                continue;
+            }
+            void* ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, handles[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();
+                ok = 0;
+            } else {
+                peer_.box[p] = ptr;
+            }
+        }
+    }
+    if (ok && cudaMalloc((void**)&peer_.ticket, 256) == cudaSuccess) cudaMemset(peer_.ticket, 0, 256);
+    else ok = 0;
+    // unanimous or not at all
+    int* flag = (int*)(stage + hs * nranks_);
+    if ((rc = cuda_fail(cudaMemcpyAsync(flag, &ok, sizeof(int), cudaMemcpyHostToDevice, stream_), "peer flag"))) return rc;
+    if ((rc = comm_allreduce_sum(&comm_, flag, 1, DT_I32, stream_, &err_))) return rc;
+    int total = 0;
+    if ((rc = cuda_fail(cudaMemcpyAsync(&total, flag, sizeof(int), cudaMemcpyDeviceToHost, stream_), "peer flag"))) return rc;
+    if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "peer flag"))) return rc;
+    peer_.ready = total == nranks_;
+    if (!peer_.ready) {
+        for (int p = 0; p < nranks_; ++p)
+            if (p != rank_ && peer_.box[p]) cudaIpcCloseMemHandle(peer_.box[p]);
+        if (peer_.mine) cudaFree(peer_.mine);
+        if (peer_.ticket) cudaFree(peer_.ticket);
+        peer_ = PeerState();
+    }
+    return CN_OK;
+}
+
+void Context::bind_peers(CnGroupArgs* a) {
+    a->peer_n = 0;
+    if (!peer_.ready) return;
+    for (int p = 0; p < nranks_; ++p) a->peer_box[p] = peer_.box[p];
+    a->peer_rank = rank_;
+    a->peer_n = nranks_;
+    a->peer_epoch = ++peer_.red_epoch;
+    a->error = error_word_;
+    waiting_launches_++;
+    stats_.peer_exchanges++;
 }
 
 int Context::mark_rank_failed(int r) {
@@ -302,6 +389,16 @@ int Context::exchange_halo(Array* a) {
     const int64_t cnt = (int64_t)H * a->unit;
     const size_t esz = dtype_size(a->dtype);
     int rc;
+    if (peer_.ready) {
+        if ((size_t)cnt * esz <= CN_PEER_HALO_SLOT && (cnt * esz) % 8 == 0) {
+            if (has_prev || has_next)
+                if ((rc = exchange_halo_p2p(a, has_prev, has_next))) return rc;
+            a->halo_valid = true;
+            stats_.halo_exchanges++;
+            return CN_OK;
+        }
+    }
+    prof_start("halo exchange (nccl)", (double)cnt * esz * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)));
     if ((rc = comm_group_start(&err_))) return rc;
     if (has_prev) {
         if ((rc = comm_send(&comm_, a->buf.data, cnt, a->dtype, rank_ - 1, stream_, &err_))) return rc;
@@ -312,8 +409,39 @@ int Context::exchange_halo(Array* a) {
         if ((rc = comm_recv(&comm_, a->buf.data + nl * a->unit * esz, cnt, a->dtype, rank_ + 1, stream_, &err_))) return rc;
     }
     if ((rc = comm_group_end(&err_))) return rc;
+    prof_stop();
     a->halo_valid = true;
     stats_.halo_exchanges++;
+    return CN_OK;
+}
+
+// Halo rows as peer stores: one small kernel pushes this rank's boundary rows into the
+// neighbours' mailboxes, publishes them with a flag, waits (bounded) for the neighbours' rows
+// and copies them into the local halo.
+int Context::exchange_halo_p2p(Array* a, bool has_prev, bool has_next) {
+    const size_t esz = dtype_size(a->dtype);
+    const size_t bytes = (size_t)a->halo * a->unit * esz;
+    const int64_t nl = a->local_rows();
+    HaloArgs h;
+    h.bytes = bytes;
+    if (has_prev) h.epoch_prev = ++peer_.epoch_prev;
+    if (has_next) h.epoch_next = ++peer_.epoch_next;
+    h.me = peer_.mine;
+    h.box_prev = has_prev ? peer_.box[rank_ - 1] : nullptr;
+    h.box_next = has_next ? peer_.box[rank_ + 1] : nullptr;
+    h.first_rows = a->buf.data;
+    h.last_rows = a->buf.data + ((size_t)nl * a->unit * esz - bytes);
+    h.halo_below = a->buf.data - bytes;
+    h.halo_above = a->buf.data + (size_t)nl * a->unit * esz;
+    h.ticket = peer_.ticket;
+    h.error = error_word_;
+    prof_start("halo exchange (peer stores)", (double)bytes * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)));
+    int rc = cuda_fail(launch_halo_exchange(h, sm_count_, stream_), "halo exchange");
+    prof_stop();
+    if (rc) return rc;
+    stats_.kernel_launches++;
+    waiting_launches_++;
+    stats_.peer_exchanges++;
     return CN_OK;
 }
 

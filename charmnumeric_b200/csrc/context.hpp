@@ -91,6 +91,7 @@ struct Stats {
     long long nodes = 0;             // DAG nodes executed
     long long bytes_h2d = 0, bytes_d2h = 0;
     long long plan_hits = 0;         // DAGs served from the plan cache
+    long long peer_exchanges = 0;    // reductions finished / halos moved through the peer mailboxes
 };
 
 struct DriverApi {
@@ -161,6 +162,8 @@ public:
     void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; plans_.clear(); }
     void set_flat_prefetch(bool on) { flat_prefetch_ = on; plans_.clear(); }
     void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
+    void set_p2p(bool on) { p2p_wanted_ = on; }  // takes effect at cn_comm_init
+    bool p2p_ready() const { return peer_.ready; }
 
 private:
     int fail(int code, const std::string& msg);
@@ -185,7 +188,7 @@ private:
     int run_scalar_only(const GroupIR& g, CompiledGroup* k);
     int bind_scalars(const GroupIR& g, CnGroupArgs* a, std::vector<std::pair<Array*, Buffer>>* swaps);
     int bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::vector<Array*>* results);
-    int finish_reductions(const std::vector<Array*>& results);
+    int finish_reductions(const std::vector<Array*>& results, bool in_kernel);
     int launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes);
     void prof_start(const std::string& label, double bytes);
     void prof_stop();
@@ -197,6 +200,9 @@ private:
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);
     int exchange_halo(Array* a);
+    int exchange_halo_p2p(Array* a, bool has_prev, bool has_next);
+    int setup_peer_boxes();
+    void bind_peers(CnGroupArgs* a);
     int ensure_scratch(size_t bytes);
     int encode_tensor_map(const Array& x, const CompiledGroup& k, const GroupIR& g, CnGroupArgs* a);
     int check_device_error();
@@ -218,12 +224,25 @@ private:
     cudaStream_t stream_ = nullptr;
     cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
     Comm comm_;
+    // Peer mailboxes (one per rank, mapped into every rank of the box through CUDA IPC):
+    // reductions finish inside the producing kernel and halos travel as peer stores, with
+    // NCCL as the fallback when the mapping cannot be set up.
+    struct PeerState {
+        bool ready = false;
+        void* mine = nullptr;                 // this rank's CnPeerBox + payload slots
+        void* box[CN_MAX_PEERS] = {nullptr};  // every rank's box as mapped here (box[rank_] == mine)
+        unsigned long long red_epoch = 0;             // fused reductions so far (all ranks take part in each)
+        unsigned long long epoch_prev = 0, epoch_next = 0;  // halo exchanges with rank - 1 / rank + 1
+        unsigned int* ticket = nullptr;       // block counter of the halo kernel
+    } peer_;
+    bool p2p_wanted_ = true;
+    long long waiting_launches_ = 0;          // launches that contain a bounded wait (TMA, peers)
+    long long checked_launches_ = 0;          // of which already covered by an error-word check
     std::vector<bool> failed_;
     DriverApi drv_;
     TileConfig tile_;
     TileConfig staged_tile_;   // tile shape of the TMA-staged stencil kernels
     unsigned int* error_word_ = nullptr;  // set by a kernel whose bounded wait ran out
-    long long staged_checked_ = 0;        // staged launches already covered by an error check
 
     std::unordered_map<int, Array> arrays_;
     std::unordered_map<std::string, CompiledGroup> kernels_;

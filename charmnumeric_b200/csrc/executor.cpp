@@ -166,7 +166,10 @@ int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block,
     if (rc) return rc;
     stats_.kernel_launches++;
     stats_.group_launches++;
-    if (k->smem_bytes) stats_.staged_launches++;
+    if (k->smem_bytes) {
+        stats_.staged_launches++;
+        waiting_launches_++;
+    }
     return CN_OK;
 }
 
@@ -272,11 +275,17 @@ int Context::bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::ve
         a->red[q] = r->buf.data;
         results->push_back(r);
     }
+    // with peer mailboxes the kernel's last block also adds up the other ranks' totals
+    if (nranks_ > 1) bind_peers(a);
     return CN_OK;
 }
 
-int Context::finish_reductions(const std::vector<Array*>& results) {
+int Context::finish_reductions(const std::vector<Array*>& results, bool in_kernel) {
     if (nranks_ == 1) return CN_OK;
+    if (in_kernel && peer_.ready) {  // already summed over the ranks inside the kernel
+        stats_.allreduces += (long long)results.size();
+        return CN_OK;
+    }
     if (!comm_.ready && !results.empty()) return fail(CN_ERR_COMM, "reduction across ranks needs cn_comm_init first");
     for (Array* r : results) {
         int rc = comm_allreduce_sum(&comm_, r->buf.data, 1, r->dtype, stream_, &err_);
@@ -493,7 +502,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         free_buffer(&sw.first->buf);
         sw.first->buf = sw.second;
     }
-    return finish_reductions(results);
+    return finish_reductions(results, true);
 }
 
 int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
@@ -638,7 +647,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
         free_buffer(&sw.first->buf);
         sw.first->buf = sw.second;
     }
-    return finish_reductions(results);
+    return finish_reductions(results, true);
 }
 
 // ---- non-fusible nodes --------------------------------------------------------------------
@@ -695,7 +704,7 @@ int Context::execute_reduce(const AstNode& r) {
     if (rc) return rc;
     stats_.kernel_launches++;
     std::vector<Array*> results{res};
-    return finish_reductions(results);
+    return finish_reductions(results, false);
 }
 
 // y = A @ x for a 2-D matrix and a 1-D vector; A is row-partitioned, x is gathered to every
@@ -850,15 +859,16 @@ int Context::synchronize() {
 
 // A staged kernel whose bounded wait on a tile ran out leaves 1 in the error word.
 int Context::check_device_error() {
-    if (stats_.staged_launches == staged_checked_) return CN_OK;
-    staged_checked_ = stats_.staged_launches;
+    if (waiting_launches_ == checked_launches_) return CN_OK;
+    checked_launches_ = waiting_launches_;
     unsigned int word = 0;
     int rc = cuda_fail(cudaMemcpyAsync(&word, error_word_, sizeof(word), cudaMemcpyDeviceToHost, stream_), "error word");
     if (rc) return rc;
     if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize"))) return rc;
     if (word) {
         cudaMemsetAsync(error_word_, 0, sizeof(word), stream_);
-        return fail(CN_ERR_CUDA, "a stencil kernel gave up waiting for a tile copy (results are incomplete)");
+        return fail(CN_ERR_CUDA, word == 1 ? "a stencil kernel gave up waiting for a tile copy (results are incomplete)"
+                                           : "a kernel gave up waiting for another GPU's data (results are incomplete)");
     }
     return CN_OK;
 }

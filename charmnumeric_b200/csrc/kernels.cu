@@ -2,6 +2,8 @@
 // sum with the deterministic two-pass finish, and the row-block matrix-vector product.
 // All of them are bandwidth-bound; none uses tensor cores (no path here is a dense
 // contraction with reuse).
+#include <algorithm>
+
 #include "cn_device.cuh"
 #include "cn_types.hpp"
 #include "kernels.hpp"
@@ -333,6 +335,90 @@ cudaError_t launch_matvec(const void* A, int64_t lda, const void* x, void* y, in
         case DT_I32: matvec_generic_kernel<int><<<grid, 256, 0, s>>>((const int*)A, lda, (const int*)x, (int*)y, rows, cols); break;
         default: matvec_generic_kernel<long long><<<grid, 256, 0, s>>>((const long long*)A, lda, (const long long*)x, (long long*)y, rows, cols); break;
     }
+    return cudaGetLastError();
+}
+
+// ---- halo exchange over peer mappings ---------------------------------------------------------
+// Phase 1: all blocks store this rank's boundary rows into the neighbours' payload slots; each
+// block fences, then draws a ticket, and the block with the last ticket publishes the payload
+// with a release store of the epoch into the neighbours' flags.  Phase 2: every block waits
+// (bounded) until the neighbours' rows for this epoch have arrived in this rank's own mailbox
+// and copies them into the local halo rows.  The grid never exceeds one block per SM, so all
+// blocks are resident and phase 1 always completes before anyone can wait for long.
+namespace {
+
+static_assert(sizeof(CnPeerBox) == 4096, "mailbox header is one page");
+
+__device__ __forceinline__ char* halo_slot(void* box, int bank, int dir) {
+    return (char*)box + sizeof(CnPeerBox) + (size_t)(bank * 2 + dir) * CN_PEER_HALO_SLOT;
+}
+
+__device__ __forceinline__ void halo_copy(char* dst, const char* src, size_t bytes, bool vec16) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    if (vec16) {
+        const size_t n = bytes / 16;
+        for (size_t i = tid; i < n; i += nth) ((int4*)dst)[i] = ((const int4*)src)[i];
+    } else {
+        const size_t n = bytes / 8;
+        for (size_t i = tid; i < n; i += nth) ((long long*)dst)[i] = ((const long long*)src)[i];
+    }
+}
+
+__device__ __forceinline__ void halo_unpack(char* dst, const char* src, size_t bytes, bool vec16) {
+    // the payload was written by another GPU: read it past L1
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    if (vec16) {
+        for (size_t i = tid; i < bytes / 16; i += nth) ((int4*)dst)[i] = __ldcv(((const int4*)src) + i);
+    } else {
+        for (size_t i = tid; i < bytes / 8; i += nth) ((long long*)dst)[i] = __ldcv(((const long long*)src) + i);
+    }
+}
+
+__global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_push, int vec_pull) {
+    __shared__ int arrived;
+    const int bp = (int)(h.epoch_prev & 1ULL), bn = (int)(h.epoch_next & 1ULL);
+    // rows for the rank below arrive there "from above" (dir 1), and the other way round
+    if (h.box_prev) halo_copy(halo_slot(h.box_prev, bp, 1), h.first_rows, h.bytes, vec_push != 0);
+    if (h.box_next) halo_copy(halo_slot(h.box_next, bn, 0), h.last_rows, h.bytes, vec_push != 0);
+    __syncthreads();
+    // One thread per block orders the block's stores (the barrier makes them its predecessors)
+    // before its ticket; the release stores of the last ticket holder then publish everything.
+    if (threadIdx.x == 0) {
+        int last = 1;
+        if (gridDim.x > 1) {
+            __threadfence_system();
+            last = atomicAdd(h.ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+        }
+        if (last) {
+            if (h.box_prev) cn_st_release_sys(&((CnPeerBox*)h.box_prev)->halo_flag[bp][1], h.epoch_prev);
+            if (h.box_next) cn_st_release_sys(&((CnPeerBox*)h.box_next)->halo_flag[bn][0], h.epoch_next);
+            if (gridDim.x > 1) *h.ticket = 0u;
+        }
+        CnPeerBox* me = (CnPeerBox*)h.me;
+        bool ok = true;
+        if (h.box_prev) ok = cn_peer_wait(&me->halo_flag[bp][0], h.epoch_prev) && ok;
+        if (h.box_next) ok = cn_peer_wait(&me->halo_flag[bn][1], h.epoch_next) && ok;
+        arrived = ok ? 1 : 0;
+        if (!ok && h.error) atomicExch(h.error, 2u);
+    }
+    __syncthreads();
+    if (!arrived) return;
+    if (h.box_prev) halo_unpack(h.halo_below, halo_slot(h.me, bp, 0), h.bytes, vec_pull != 0);
+    if (h.box_next) halo_unpack(h.halo_above, halo_slot(h.me, bn, 1), h.bytes, vec_pull != 0);
+}
+
+}  // namespace
+
+cudaError_t launch_halo_exchange(const HaloArgs& h, int sm_count, cudaStream_t s) {
+    if (h.bytes == 0 || (!h.box_prev && !h.box_next)) return cudaSuccess;
+    if (h.bytes % 8 || h.bytes > CN_PEER_HALO_SLOT) return cudaErrorInvalidValue;
+    const bool vec_push = h.bytes % 16 == 0 && (((uintptr_t)h.first_rows | (uintptr_t)h.last_rows) & 15) == 0;
+    const bool vec_pull = h.bytes % 16 == 0 && (((uintptr_t)h.halo_below | (uintptr_t)h.halo_above) & 15) == 0;
+    long long blocks = (long long)((h.bytes + 256 * 64 - 1) / (256 * 64));  // 64 bytes per thread
+    int grid = (int)std::max<long long>(1, std::min<long long>(blocks, sm_count > 0 ? sm_count : 148));
+    halo_exchange_kernel<<<grid, 256, 0, s>>>(h, vec_push ? 1 : 0, vec_pull ? 1 : 0);
     return cudaGetLastError();
 }
 

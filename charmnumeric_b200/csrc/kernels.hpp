@@ -32,4 +32,23 @@ cudaError_t launch_dot(const void* a, const void* b, int64_t n, int dtype, void*
 cudaError_t launch_matvec(const void* A, int64_t lda, const void* x, void* y, int64_t rows,
                           int64_t cols, int dtype, cudaStream_t s);
 
+// Halo exchange through the peer mailboxes (takes the place of the per-edge messages of
+// src/executor_core.cpp:7-143 and PartitionImpl::receive_data, src/partition_comm.cpp:25-61).
+// Rows are 8-byte multiples; pointers of absent neighbours are null.
+struct HaloArgs {
+    const char* first_rows = nullptr;  // this rank's first `halo` rows (go to the rank below)
+    const char* last_rows = nullptr;   // this rank's last `halo` rows (go to the rank above)
+    char* halo_below = nullptr;        // local halo rows filled from the rank below
+    char* halo_above = nullptr;        // local halo rows filled from the rank above
+    void* me = nullptr;                // this rank's mailbox
+    void* box_prev = nullptr;          // mailbox of rank - 1 as mapped here (null: none)
+    void* box_next = nullptr;          // mailbox of rank + 1 as mapped here (null: none)
+    size_t bytes = 0;                  // bytes per direction
+    // exchanges are counted per neighbour pair (both sides count alike); the parity picks the bank
+    unsigned long long epoch_prev = 0, epoch_next = 0;
+    unsigned int* ticket = nullptr;    // zeroed block counter, left at zero
+    unsigned int* error = nullptr;     // device error word
+};
+cudaError_t launch_halo_exchange(const HaloArgs& h, int sm_count, cudaStream_t s);
+
 }  // namespace cn

@@ -165,6 +165,7 @@ typedef struct cn_stats {
     int64_t bytes_h2d;
     int64_t bytes_d2h;
     int64_t plan_hits;         /* DAGs whose bytes had run before (parsing and lowering skipped) */
+    int64_t peer_exchanges;    /* reductions finished in-kernel / halos moved through peer mailboxes */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
@@ -174,7 +175,10 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
  * tiles: never / 3-D groups only (default) / 2-D groups too; process-wide), "staged_tile_tx" /
  * "staged_tile_rows", "profile" 0/1, "plan_cache" 0/1 (default 1: a DAG blob whose bytes,
  * epoch aside, have run before skips parsing and lowering), "flat_prefetch" 0/1 (default 0:
- * flat kernels request the next tile's inputs before the arithmetic of the current one). */
+ * flat kernels request the next tile's inputs before the arithmetic of the current one),
+ * "p2p" 0/1 (default 1; read by cn_comm_init: map every rank's mailbox into every other rank
+ * with CUDA IPC, finish reductions inside the producing kernel and move halo rows as NVLink
+ * peer stores; when the mapping cannot be set up on all ranks, NCCL does both). */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus

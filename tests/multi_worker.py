@@ -71,6 +71,7 @@ def main():
     st = itf.context.stats()
     result["halo_exchanges"] = np.array(st["halo_exchanges"])
     result["allreduces"] = np.array(st["allreduces"])
+    result["peer_exchanges"] = np.array(st["peer_exchanges"])
     np.savez(os.path.join(outdir, f"{case}_rank{rank}.npz"), **result)
     itf.close()
 

@@ -1,6 +1,8 @@
-"""Multi-GPU parity: one process per GPU (slab partition, NCCL halo exchange and allreduce),
-each rank fetches the whole result and compares it with the oracle that ran the same DAG.
-Needs at least two GPUs; skipped otherwise."""
+"""Multi-GPU parity: one process per GPU (slab partition; halo rows and reduction totals travel
+through the peer mailboxes over NVLink, or through NCCL send/recv and allreduce when the peer
+path is switched off), each rank fetches the whole result and compares it with the oracle that
+ran the same DAG.  Needs at least two GPUs; skipped otherwise."""
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -17,15 +19,12 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("case", ["jacobi2d", "jacobi2d_small", "jacobi3d", "cg", "chain", "matvec", "diag"])
-@pytest.mark.parametrize("nranks", [2, 4])
-def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
-    if _gpu_count() < nranks:
-        pytest.skip(f"needs {nranks} GPUs")
+def _run_ranks(tmp_path, case, nranks, p2p):
     idfile = str(tmp_path / "nccl_id")
+    env = dict(os.environ, CN_P2P=str(p2p))
     procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "multi_worker.py"), str(r), str(nranks),
                                idfile, str(tmp_path), case], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
-                              text=True) for r in range(nranks)]
+                              text=True, env=env) for r in range(nranks)]
     outputs = []
     for p in procs:
         try:
@@ -37,9 +36,12 @@ def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
         outputs.append(out)
     for r, p in enumerate(procs):
         assert p.returncode == 0, f"rank {r} failed:\n{outputs[r][-3000:]}"
+    return [np.load(tmp_path / f"{case}_rank{r}.npz") for r in range(nranks)]
+
+
+def _check(case, results, p2p):
     exact = case.startswith("jacobi")
-    for r in range(nranks):
-        d = np.load(tmp_path / f"{case}_rank{r}.npz")
+    for r, d in enumerate(results):
         for key in d.files:
             if not key.startswith("gpu_"):
                 continue
@@ -51,3 +53,28 @@ def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
                 assert np.max(np.abs(g - c)) <= 1e-10 * scale, (case, r, key)
         if case in ("jacobi2d", "jacobi3d", "cg"):
             assert int(d["halo_exchanges"]) > 0
+        if case in ("jacobi2d", "jacobi3d", "cg", "chain"):
+            # the peer path was really taken (or really not)
+            assert (int(d["peer_exchanges"]) > 0) == bool(p2p), (case, r)
+    # reduction results are summed in rank order on every rank: identical bits everywhere
+    if p2p:
+        for key in results[0].files:
+            if key.startswith("gpu_") and results[0][key].size == 1:
+                for d in results[1:]:
+                    assert d[key].tobytes() == results[0][key].tobytes(), (case, key)
+
+
+@pytest.mark.parametrize("case", ["jacobi2d", "jacobi2d_small", "jacobi3d", "cg", "chain", "matvec", "diag"])
+@pytest.mark.parametrize("nranks", [2, 4])
+def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
+    if _gpu_count() < nranks:
+        pytest.skip(f"needs {nranks} GPUs")
+    _check(case, _run_ranks(tmp_path, case, nranks, 1), 1)
+
+
+@pytest.mark.parametrize("case", ["jacobi2d", "jacobi3d", "cg", "chain"])
+def test_multi_gpu_nccl_transport(tmp_path, case):
+    """The same programs with the peer mailboxes switched off: NCCL moves halos and totals."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _check(case, _run_ranks(tmp_path, case, 2, 0), 0)
