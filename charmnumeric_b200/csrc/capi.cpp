@@ -242,6 +242,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         ctx->impl.set_staged_tile(-1, (int)value);
     } else if (k == "debug_drop_copies") {
         ctx->impl.set_debug_drop_copies(value != 0);
+    } else if (k == "debug_peer_wait") {
+        return ctx->impl.debug_peer_wait();
     } else if (k == "p2p") {
         ctx->impl.set_p2p(value != 0);
     } else if (k == "plan_cache") {

@@ -238,8 +238,9 @@ __device__ __forceinline__ unsigned long long cn_ld_acquire_sys(const unsigned l
 }
 
 // true once *flag >= epoch; false when the bound ran out
-__device__ __forceinline__ bool cn_peer_wait(const unsigned long long* flag, unsigned long long epoch) {
-    for (unsigned int i = 0; i < CN_PEER_WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool cn_peer_wait(const unsigned long long* flag, unsigned long long epoch,
+                                             unsigned int limit = CN_PEER_WAIT_LIMIT) {
+    for (unsigned int i = 0; i < limit; ++i) {
         if (cn_ld_acquire_sys(flag) >= epoch) return true;
         __nanosleep(40);
     }

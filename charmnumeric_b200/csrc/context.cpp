@@ -445,6 +445,41 @@ int Context::exchange_halo_p2p(Array* a, bool has_prev, bool has_next) {
     return CN_OK;
 }
 
+// Test hook for the failure path of the peer transport, without a second GPU and without
+// hanging anything: one halo exchange against a scratch mailbox that plays both this rank and
+// its neighbour.  The kernel publishes its rows, then waits for rows that nobody sends; the
+// short bound runs out, the kernel sets the error word and returns, and the next synchronise
+// reports it as a status code.
+int Context::debug_peer_wait() {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    cudaSetDevice(device_);
+    const size_t box_bytes = sizeof(CnPeerBox) + 4ull * CN_PEER_HALO_SLOT;
+    void* box = nullptr;
+    unsigned int* ticket = nullptr;
+    int rc = cuda_fail(cudaMalloc(&box, box_bytes), "scratch mailbox");
+    if (rc) return rc;
+    if ((rc = cuda_fail(cudaMalloc((void**)&ticket, 256), "scratch mailbox"))) return rc;
+    cudaMemsetAsync(box, 0, sizeof(CnPeerBox) + 64, stream_);
+    cudaMemsetAsync(ticket, 0, 256, stream_);
+    HaloArgs h;
+    h.bytes = 64;
+    h.epoch_prev = 2;
+    h.me = box;
+    h.box_prev = box;
+    h.first_rows = (const char*)box + sizeof(CnPeerBox);      // any 64 readable bytes
+    h.halo_below = (char*)box + sizeof(CnPeerBox) + 256;
+    h.ticket = ticket;
+    h.error = error_word_;
+    h.wait_limit = 20000;
+    rc = cuda_fail(launch_halo_exchange(h, sm_count_, stream_), "halo exchange");
+    waiting_launches_++;
+    stats_.kernel_launches++;
+    cudaStreamSynchronize(stream_);
+    cudaFree(box);
+    cudaFree(ticket);
+    return rc;
+}
+
 int Context::ensure_scratch(size_t bytes) {
     if (scratch_bytes_ >= bytes) return CN_OK;
     if (scratch_) {

@@ -137,6 +137,7 @@ public:
     void set_profile(bool on) { profile_ = on; }
     int profile_report(char* buf, int64_t cap);
     int mark_rank_failed(int r);
+    int debug_peer_wait();  // test hook: a halo exchange whose partner never answers
     int array_info(int name, int* ndims, int64_t* shape, int* dtype, int64_t* row_begin,
                    int64_t* row_end);
 

@@ -398,8 +398,9 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_
         }
         CnPeerBox* me = (CnPeerBox*)h.me;
         bool ok = true;
-        if (h.box_prev) ok = cn_peer_wait(&me->halo_flag[bp][0], h.epoch_prev) && ok;
-        if (h.box_next) ok = cn_peer_wait(&me->halo_flag[bn][1], h.epoch_next) && ok;
+        const unsigned int limit = h.wait_limit ? h.wait_limit : CN_PEER_WAIT_LIMIT;
+        if (h.box_prev) ok = cn_peer_wait(&me->halo_flag[bp][0], h.epoch_prev, limit) && ok;
+        if (h.box_next) ok = cn_peer_wait(&me->halo_flag[bn][1], h.epoch_next, limit) && ok;
         arrived = ok ? 1 : 0;
         if (!ok && h.error) atomicExch(h.error, 2u);
     }

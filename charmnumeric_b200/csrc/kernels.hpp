@@ -48,6 +48,7 @@ struct HaloArgs {
     unsigned long long epoch_prev = 0, epoch_next = 0;
     unsigned int* ticket = nullptr;    // zeroed block counter, left at zero
     unsigned int* error = nullptr;     // device error word
+    unsigned int wait_limit = 0;       // polls before a wait gives up (0: the default bound)
 };
 cudaError_t launch_halo_exchange(const HaloArgs& h, int sm_count, cudaStream_t s);
 

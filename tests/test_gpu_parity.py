@@ -410,6 +410,22 @@ def test_bounded_device_wait_reports_status(interface):
     assert_bit_exact(gpu, cpu)
 
 
+def test_bounded_peer_wait_reports_status(interface):
+    """Failure path of the cross-GPU transport on one GPU: a halo exchange against a scratch
+    mailbox whose partner never answers.  The kernel's bounded wait runs out, it sets the error
+    word and returns; the next synchronise reports a status code and the context stays usable."""
+    from charmnumeric_b200._lib import CnError
+    ctx = interface.context
+    ctx.synchronize()
+    ctx.set_option("debug_peer_wait", 1)
+    with pytest.raises(CnError) as e:
+        ctx.synchronize()
+    assert e.value.status == 8 and "another GPU" in e.value.message
+    ctx.synchronize()
+    a = cnp.ones((32,))
+    assert np.array_equal((a + a).get(interface), np.full(32, 2.0))
+
+
 def test_rank_marked_failed_stops_collective_work():
     """Host-side failure notice: once a rank is marked failed, DAG submission returns
     CN_STATUS_RANK_FAILED instead of enqueuing work that would wait for that rank."""
