@@ -29,6 +29,7 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
     if (const char* f = getenv("CN_FLAT_PREFETCH")) flat_prefetch_ = atoi(f) != 0;
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
+    if (const char* f = getenv("CN_OVERLAP_HALO")) overlap_halo_ = atoi(f) != 0;
     staged_tile_.tx = 64;
     staged_tile_.r = 4;
     if (const char* n = getenv("CN_STAGED_NS")) {
@@ -65,6 +66,12 @@ Context::~Context() {
         cudaFree(peer_.ticket);
         // peer_.mine is not freed here: another rank may still hold a mapping of it, and
         // freeing exported memory under a live mapping is undefined; it goes with the process
+    }
+    if (stream2_) {
+        cudaStreamSynchronize(stream2_);
+        cudaStreamDestroy(stream2_);
+        cudaEventDestroy(ev_fork_);
+        cudaEventDestroy(ev_join_);
     }
     if (ev_start_) cudaEventDestroy(ev_start_);
     if (ev_stop_) cudaEventDestroy(ev_stop_);
@@ -367,7 +374,18 @@ int Context::mark_rank_failed(int r) {
     return CN_OK;
 }
 
-int Context::exchange_halo(Array* a) {
+int Context::ensure_second_stream() {
+    if (stream2_) return CN_OK;
+    int rc;
+    // highest priority: its few blocks (halo rows, edge rows) should get the first free SM slots
+    int least = 0, greatest = 0;
+    cudaDeviceGetStreamPriorityRange(&least, &greatest);
+    if ((rc = cuda_fail(cudaStreamCreateWithPriority(&stream2_, cudaStreamNonBlocking, greatest), "second stream"))) return rc;
+    if ((rc = cuda_fail(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming), "event"))) return rc;
+    return cuda_fail(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming), "event");
+}
+
+int Context::exchange_halo(Array* a, cudaStream_t st) {
     if (nranks_ == 1 || a->replicated || a->halo_valid) return CN_OK;
     if (!comm_.ready) return fail(CN_ERR_COMM, "halo exchange needs cn_comm_init first");
     const int H = a->halo;
@@ -392,21 +410,21 @@ int Context::exchange_halo(Array* a) {
     if (peer_.ready) {
         if ((size_t)cnt * esz <= CN_PEER_HALO_SLOT && (cnt * esz) % 8 == 0) {
             if (has_prev || has_next)
-                if ((rc = exchange_halo_p2p(a, has_prev, has_next))) return rc;
+                if ((rc = exchange_halo_p2p(a, has_prev, has_next, st))) return rc;
             a->halo_valid = true;
             stats_.halo_exchanges++;
             return CN_OK;
         }
     }
-    prof_start("halo exchange (nccl)", (double)cnt * esz * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)));
+    prof_start("halo exchange (nccl)", (double)cnt * esz * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)), st);
     if ((rc = comm_group_start(&err_))) return rc;
     if (has_prev) {
-        if ((rc = comm_send(&comm_, a->buf.data, cnt, a->dtype, rank_ - 1, stream_, &err_))) return rc;
-        if ((rc = comm_recv(&comm_, a->buf.data - cnt * esz, cnt, a->dtype, rank_ - 1, stream_, &err_))) return rc;
+        if ((rc = comm_send(&comm_, a->buf.data, cnt, a->dtype, rank_ - 1, st, &err_))) return rc;
+        if ((rc = comm_recv(&comm_, a->buf.data - cnt * esz, cnt, a->dtype, rank_ - 1, st, &err_))) return rc;
     }
     if (has_next) {
-        if ((rc = comm_send(&comm_, a->buf.data + (nl * a->unit - cnt) * esz, cnt, a->dtype, rank_ + 1, stream_, &err_))) return rc;
-        if ((rc = comm_recv(&comm_, a->buf.data + nl * a->unit * esz, cnt, a->dtype, rank_ + 1, stream_, &err_))) return rc;
+        if ((rc = comm_send(&comm_, a->buf.data + (nl * a->unit - cnt) * esz, cnt, a->dtype, rank_ + 1, st, &err_))) return rc;
+        if ((rc = comm_recv(&comm_, a->buf.data + nl * a->unit * esz, cnt, a->dtype, rank_ + 1, st, &err_))) return rc;
     }
     if ((rc = comm_group_end(&err_))) return rc;
     prof_stop();
@@ -418,7 +436,7 @@ int Context::exchange_halo(Array* a) {
 // Halo rows as peer stores: one small kernel pushes this rank's boundary rows into the
 // neighbours' mailboxes, publishes them with a flag, waits (bounded) for the neighbours' rows
 // and copies them into the local halo.
-int Context::exchange_halo_p2p(Array* a, bool has_prev, bool has_next) {
+int Context::exchange_halo_p2p(Array* a, bool has_prev, bool has_next, cudaStream_t st) {
     const size_t esz = dtype_size(a->dtype);
     const size_t bytes = (size_t)a->halo * a->unit * esz;
     const int64_t nl = a->local_rows();
@@ -435,8 +453,8 @@ int Context::exchange_halo_p2p(Array* a, bool has_prev, bool has_next) {
     h.halo_above = a->buf.data + (size_t)nl * a->unit * esz;
     h.ticket = peer_.ticket;
     h.error = error_word_;
-    prof_start("halo exchange (peer stores)", (double)bytes * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)));
-    int rc = cuda_fail(launch_halo_exchange(h, sm_count_, stream_), "halo exchange");
+    prof_start("halo exchange (peer stores)", (double)bytes * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)), st);
+    int rc = cuda_fail(launch_halo_exchange(h, sm_count_, st), "halo exchange");
     prof_stop();
     if (rc) return rc;
     stats_.kernel_launches++;

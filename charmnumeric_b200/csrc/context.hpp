@@ -92,6 +92,7 @@ struct Stats {
     long long bytes_h2d = 0, bytes_d2h = 0;
     long long plan_hits = 0;         // DAGs served from the plan cache
     long long peer_exchanges = 0;    // reductions finished / halos moved through the peer mailboxes
+    long long overlapped_sweeps = 0; // stencil sweeps whose interior ran beside the halo exchange
 };
 
 struct DriverApi {
@@ -163,6 +164,7 @@ public:
     void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; plans_.clear(); }
     void set_flat_prefetch(bool on) { flat_prefetch_ = on; plans_.clear(); }
     void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
+    void set_overlap_halo(bool on) { overlap_halo_ = on; }
     void set_p2p(bool on) { p2p_wanted_ = on; }  // takes effect at cn_comm_init
     bool p2p_ready() const { return peer_.ready; }
 
@@ -190,8 +192,8 @@ private:
     int bind_scalars(const GroupIR& g, CnGroupArgs* a, std::vector<std::pair<Array*, Buffer>>* swaps);
     int bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::vector<Array*>* results);
     int finish_reductions(const std::vector<Array*>& results, bool in_kernel);
-    int launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes);
-    void prof_start(const std::string& label, double bytes);
+    int launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes, cudaStream_t st = nullptr);
+    void prof_start(const std::string& label, double bytes, cudaStream_t st = nullptr);
     void prof_stop();
     int get_kernel(const GroupIR& g, CompiledGroup** out);
     int execute_reduce(const AstNode& root);
@@ -200,8 +202,9 @@ private:
     int execute_diag(const AstNode& root);
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);
-    int exchange_halo(Array* a);
-    int exchange_halo_p2p(Array* a, bool has_prev, bool has_next);
+    int exchange_halo(Array* a, cudaStream_t st);
+    int exchange_halo_p2p(Array* a, bool has_prev, bool has_next, cudaStream_t st);
+    int ensure_second_stream();
     int setup_peer_boxes();
     void bind_peers(CnGroupArgs* a);
     int ensure_scratch(size_t bytes);
@@ -223,6 +226,13 @@ private:
     bool initialised_ = false;
     int sm_count_ = 148;
     cudaStream_t stream_ = nullptr;
+    // second stream of the overlapped sweeps: halo exchange and the slab's edge rows run here
+    // while the interior runs on stream_; it is always joined back before anything else happens
+    cudaStream_t stream2_ = nullptr;
+    cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
+    cudaStream_t prof_stream_ = nullptr;
+    bool overlap_halo_ = false;  // measured: no gain at 2048^2, a loss at 1024^3 (the halo kernel's
+                                 // blocks queue behind the persistent interior blocks)
     cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
     Comm comm_;
     // Peer mailboxes (one per rank, mapped into every rank of the box through CUDA IPC):

@@ -108,7 +108,8 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     return CN_OK;
 }
 
-void Context::prof_start(const std::string& label, double bytes) {
+void Context::prof_start(const std::string& label, double bytes, cudaStream_t st) {
+    if (!st) st = stream_;
     if (!profile_) return;
     ProfEntry& e = prof_[label];
     e.launches++;
@@ -116,14 +117,15 @@ void Context::prof_start(const std::string& label, double bytes) {
     cudaEvent_t a = nullptr, b = nullptr;
     cudaEventCreate(&a);
     cudaEventCreate(&b);
-    cudaEventRecord(a, stream_);
+    cudaEventRecord(a, st);
     e.events.push_back({a, b});
     prof_open_ = &e;
+    prof_stream_ = st;
 }
 
 void Context::prof_stop() {
     if (!profile_ || !prof_open_) return;
-    cudaEventRecord(prof_open_->events.back().second, stream_);
+    cudaEventRecord(prof_open_->events.back().second, prof_stream_);
     prof_open_ = nullptr;
 }
 
@@ -155,12 +157,13 @@ int Context::profile_report(char* buf, int64_t cap) {
     return CN_OK;
 }
 
-int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes) {
+int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block, double bytes, cudaStream_t st) {
+    if (!st) st = stream_;
     void* params[] = {(void*)&a};
-    prof_start(k->label, bytes);
+    prof_start(k->label, bytes, st);
     int rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1,
                                            (unsigned)k->smem_bytes,
-                                           (CUstream)stream_, params, nullptr),
+                                           (CUstream)st, params, nullptr),
                          "cuLaunchKernel");
     prof_stop();
     if (rc) return rc;
@@ -346,14 +349,22 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     if (!ref) return fail(CN_ERR_UNSUPPORTED, "group touches no array");
 
     // halos: a leaf shifted along dimension 0 reads rows owned by a neighbour
+    std::vector<Array*> stale;
     if (nranks_ > 1 && !ref->replicated) {
         if (g.max_halo > halo_) return fail(CN_ERR_UNSUPPORTED, "stencil reaches further along dimension 0 than the halo depth");
         for (auto& l : g.leaves)
             if (l.delta[0] != 0) {
                 Array* x = find(l.name);
-                if ((rc = exchange_halo(x))) return rc;
+                if (!x->halo_valid && std::find(stale.begin(), stale.end(), x) == stale.end()) stale.push_back(x);
             }
     }
+    // Without a fused reduction the sweep can be cut along dimension 0: the rows next to the
+    // slab edges wait for the neighbours' halo rows on a second stream while the interior,
+    // which needs none of them, runs on the main stream.
+    const bool overlap = overlap_halo_ && !stale.empty() && g.reds.empty() && g.souts.empty() && !g.flat;
+    if (!overlap)
+        for (Array* x : stale)
+            if ((rc = exchange_halo(x, stream_))) return rc;
 
     for (size_t i = 0; i < ins.size(); ++i) a.in[i] = ins[i]->buf.data;
     for (size_t m = 0; m < outs.size(); ++m) {
@@ -380,13 +391,15 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     hi[0] = std::min(hi[0], re) - rb;
     rlo[0] = std::max(rlo[0], rb) - rb;
     rhi[0] = std::min(rhi[0], re) - rb;
-    bool empty = false;
-    for (int d = 0; d < nd; ++d)
-        if (hi[d] <= lo[d]) empty = true;
-
     int64_t strides[3];
     array_strides(*ref, strides);
     const int V = g.vec;
+    // Tiles and grid of one launch over the box [lo, hi) (local coordinates).
+    auto plan = [&](const int64_t* lo, const int64_t* hi, CnGroupArgs& a, int* grid_out, int64_t* ntiles_out,
+                    bool* empty_out) -> int {
+    bool empty = false;
+    for (int d = 0; d < nd; ++d)
+        if (hi[d] <= lo[d]) empty = true;
     int64_t ntiles = 0;
     if (g.flat) {
         int64_t n = ref->local_elems();
@@ -453,7 +466,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
             }
         }
     }
-    if (ntiles >= (1LL << 31)) return fail(CN_ERR_LIMIT, "too many tiles for one launch");
+        if (ntiles >= (1LL << 31)) return fail(CN_ERR_LIMIT, "too many tiles for one launch");
     if (g.staged) {
         Array* sx = find(g.stage_array);
         if (!sx) return fail(CN_ERR_UNKNOWN_ARRAY, "stencil array vanished");
@@ -473,6 +486,16 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     }
     int grid = (int)grid64;
 
+    *grid_out = grid;
+    *ntiles_out = ntiles;
+    *empty_out = empty;
+    return CN_OK;
+    };
+    int grid = 1;
+    int64_t ntiles = 0;
+    bool empty = false;
+    if ((rc = plan(lo, hi, a, &grid, &ntiles, &empty))) return rc;
+
     std::vector<Array*> results;
     if ((rc = bind_reductions(g, &a, grid, &results))) return rc;
     // binding may have created arrays: the table can re-hash, so refresh raw pointers
@@ -491,7 +514,49 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         else for (int d = 0; d < nd; ++d) vol *= (double)std::max<int64_t>(0, hi[d] - lo[d]);
         if (empty) vol = 0;
         double bytes = vol * (double)(in_names.size() + g.outs.size()) * dtype_size(g.dtype);
-        if ((rc = launch(k, a, grid, CN_BLOCK, bytes))) return rc;
+        bool done = false;
+        if (overlap && !empty) {
+            // rows [0, H) and [nl - H, nl) of the slab read halo rows; everything between does not
+            const int64_t H = halo_, nl = re - rb;
+            const int64_t i0 = std::max<int64_t>(lo[0], H), i1 = std::min<int64_t>(hi[0], nl - H);
+            if (i1 - i0 >= 4 * H && (rc = ensure_second_stream()) == CN_OK) {
+                const double row_bytes = bytes / (double)(hi[0] - lo[0]);
+                cudaEventRecord(ev_fork_, stream_);
+                cudaStreamWaitEvent(stream2_, ev_fork_, 0);
+                for (Array* x : stale)
+                    if ((rc = exchange_halo(x, stream2_))) return rc;
+                int64_t blo[3] = {lo[0], lo[1], lo[2]}, bhi[3] = {hi[0], hi[1], hi[2]};
+                const int64_t parts[3][2] = {{lo[0], i0}, {i1, hi[0]}, {i0, i1}};
+                for (int part = 0; part < 3; ++part) {
+                    blo[0] = parts[part][0];
+                    bhi[0] = parts[part][1];
+                    if (bhi[0] <= blo[0]) continue;
+                    CnGroupArgs b = a;
+                    int bgrid = 1;
+                    int64_t bt = 0;
+                    bool be = false;
+                    if ((rc = plan(blo, bhi, b, &bgrid, &bt, &be))) return rc;
+                    if (bt > 0 && (rc = launch(k, b, bgrid, CN_BLOCK, row_bytes * (double)(bhi[0] - blo[0]),
+                                               part == 2 ? stream_ : stream2_)))
+                        return rc;
+                }
+                cudaEventRecord(ev_join_, stream2_);
+                cudaStreamWaitEvent(stream_, ev_join_, 0);
+                stats_.overlapped_sweeps++;
+                done = true;
+            } else if (rc) {
+                return rc;
+            }
+        }
+        if (!done) {
+            if (overlap)
+                for (Array* x : stale)
+                    if ((rc = exchange_halo(x, stream_))) return rc;
+            if ((rc = launch(k, a, grid, CN_BLOCK, bytes))) return rc;
+        }
+    } else if (overlap) {
+        for (Array* x : stale)
+            if ((rc = exchange_halo(x, stream_))) return rc;
     }
     for (size_t m = 0; m < outs.size(); ++m) {
         Array* x = outs[m];

@@ -166,6 +166,7 @@ typedef struct cn_stats {
     int64_t bytes_d2h;
     int64_t plan_hits;         /* DAGs whose bytes had run before (parsing and lowering skipped) */
     int64_t peer_exchanges;    /* reductions finished in-kernel / halos moved through peer mailboxes */
+    int64_t overlapped_sweeps; /* stencil sweeps whose interior ran beside the halo exchange */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
@@ -178,7 +179,10 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
  * flat kernels request the next tile's inputs before the arithmetic of the current one),
  * "p2p" 0/1 (default 1; read by cn_comm_init: map every rank's mailbox into every other rank
  * with CUDA IPC, finish reductions inside the producing kernel and move halo rows as NVLink
- * peer stores; when the mapping cannot be set up on all ranks, NCCL does both). */
+ * peer stores; when the mapping cannot be set up on all ranks, NCCL does both),
+ * "overlap_halo" 0/1 (default 0: a stencil sweep without a fused reduction is cut along
+ * dimension 0; the halo exchange and the rows next to the slab edges run on a second stream
+ * beside the interior). */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus

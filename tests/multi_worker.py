@@ -72,6 +72,7 @@ def main():
     result["halo_exchanges"] = np.array(st["halo_exchanges"])
     result["allreduces"] = np.array(st["allreduces"])
     result["peer_exchanges"] = np.array(st["peer_exchanges"])
+    result["overlapped_sweeps"] = np.array(st["overlapped_sweeps"])
     np.savez(os.path.join(outdir, f"{case}_rank{rank}.npz"), **result)
     itf.close()
 

@@ -19,9 +19,9 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-def _run_ranks(tmp_path, case, nranks, p2p):
+def _run_ranks(tmp_path, case, nranks, p2p, overlap=0):
     idfile = str(tmp_path / "nccl_id")
-    env = dict(os.environ, CN_P2P=str(p2p))
+    env = dict(os.environ, CN_P2P=str(p2p), CN_OVERLAP_HALO=str(overlap))
     procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "multi_worker.py"), str(r), str(nranks),
                                idfile, str(tmp_path), case], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                               text=True, env=env) for r in range(nranks)]
@@ -78,3 +78,15 @@ def test_multi_gpu_nccl_transport(tmp_path, case):
     if _gpu_count() < 2:
         pytest.skip("needs 2 GPUs")
     _check(case, _run_ranks(tmp_path, case, 2, 0), 0)
+
+
+@pytest.mark.parametrize("case", ["jacobi2d", "jacobi3d"])
+def test_multi_gpu_overlapped_halo(tmp_path, case):
+    """Option overlap_halo: sweeps without a fused reduction are cut along dimension 0 and the
+    interior runs on the main stream beside the halo exchange and the edge rows."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    results = _run_ranks(tmp_path, case, 2, 1, overlap=1)
+    _check(case, results, 1)
+    for d in results:
+        assert int(d["overlapped_sweeps"]) > 0
