@@ -37,7 +37,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         // a staged tile is one TMA box: at most 256 elements per side
         tile = staged_tile_;
         // measured best: 3-D march 128 columns x 8 rows per plane tile with a 4-deep ring
-        // (small slots, five blocks per SM); 2-D tiles 128 x 16
+        // (42 KB of shared memory per block, four blocks per SM); 2-D tiles 128 x 16
         if (g.ndims == 3 && !staged_tile_set_) tile.r = 2;
         if (tile.tx > 64) tile.tx = 64;
         while ((CN_BLOCK / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
