@@ -10,7 +10,7 @@ from .frontend import (  # noqa: F401
     Array, ArrayOperation, ArrayView, CharmNumericInterface, DType, add, arange, array, asarray,
     copy, copyto, create_array, diag, divide, dot, dot2d, empty, empty_like, execute, exp, eye, full,
     full_like, identity, matmul, multiply, norm2, ones, ones_like, reset_frontend_state,
-    set_auto_flush, subtract, tanh, sqrt, zeros, zeros_like)
+    set_auto_flush, subtract, tanh, tile, sqrt, zeros, zeros_like)
 from .frontend import absolute as abs  # noqa: A001,F401
 from .frontend import sum_all as sum  # noqa: A001,F401
 

@@ -694,8 +694,8 @@ int Context::execute_node(const Dag& dag, size_t* index) {
             case OP_MATMUL: last = execute_matmul(*r); break;
             case OP_RANDU: last = execute_randu(*r); break;
             case OP_DIAG: last = execute_diag(*r); break;
+            case OP_TILE: last = execute_tile(*r); break;
             case OP_MATMATMUL:
-            case OP_TILE:
             case OP_GET_REGION:
                 return fail(CN_ERR_UNSUPPORTED, "opcode " + std::to_string(r->opcode) +
                                                     " is outside this backend's scope");

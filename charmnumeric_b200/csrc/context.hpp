@@ -200,6 +200,7 @@ private:
     int execute_matmul(const AstNode& root);
     int execute_randu(const AstNode& root);
     int execute_diag(const AstNode& root);
+    int execute_tile(const AstNode& root);
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);
     int exchange_halo(Array* a, cudaStream_t st);

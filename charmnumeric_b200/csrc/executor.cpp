@@ -890,6 +890,62 @@ int Context::execute_diag(const AstNode& r) {
     return CN_OK;
 }
 
+// TILE (charmnumeric/operations.py:52-72, src/executor_transfer.cpp): the operand is repeated
+// along every dimension, with leading dimensions added when there are more repeat counts than
+// operand dimensions.  The operand is usually small: with several ranks it is gathered whole
+// onto every rank first (the same grouped broadcasts cn_get uses), then every rank fills its
+// own rows of the result.
+int Context::execute_tile(const AstNode& r) {
+    if (r.operands.size() < 2) return fail(CN_ERR_BAD_BLOB, "TILE needs (array, repeat counts...)");
+    Array* x = nullptr;
+    Region rx;
+    int rc = operand_array(r.operands[0], &x, &rx);
+    if (rc) return rc;
+    for (int d = 0; d < x->ndims; ++d)
+        if (rx.start[d] != 0 || rx.stop[d] != x->shape[d] || rx.step[d] != 1)
+            return fail(CN_ERR_UNSUPPORTED, "TILE of a view is not supported; assign the view to an array first");
+    const int nrep = (int)r.operands.size() - 1;
+    const int ond = std::max(x->ndims, nrep);
+    if (ond > kMaxDims) return fail(CN_ERR_UNSUPPORTED, "TILE result has more than three dimensions");
+    if (r.result_name == x->name) return fail(CN_ERR_HAZARD, "TILE result aliases its operand");
+    // shapes left-aligned on the result's dimensions: the operand gets leading 1s, the repeat
+    // counts too; unused trailing slots are 1
+    int64_t sshape[3] = {1, 1, 1}, oshape[3] = {1, 1, 1};
+    for (int d = 0; d < x->ndims; ++d) sshape[ond - x->ndims + d] = x->shape[d];
+    for (int d = 0; d < ond; ++d) oshape[d] = sshape[d];
+    for (int i = 0; i < nrep; ++i) {
+        const Operand& op = r.operands[1 + i];
+        if (op.is_ref || !op.leaf || !op.leaf->is_scalar) return fail(CN_ERR_BAD_BLOB, "TILE repeat counts must be literal scalars");
+        const int64_t rep = (int64_t)op.leaf->scalar;
+        if (rep < 1) return fail(CN_ERR_INVALID_ARGUMENT, "TILE repeat counts must be positive");
+        oshape[ond - nrep + i] *= rep;
+    }
+    const int dtype = x->dtype, xname = x->name;
+    const size_t esz = dtype_size(dtype);
+    Array* out = nullptr;
+    if ((rc = create_array(r.result_name, ond, oshape, dtype, false, &out))) return rc;
+    x = find(xname);
+    const void* src = x->buf.data;
+    if (nranks_ > 1 && !x->replicated) {
+        if (!comm_.ready) return fail(CN_ERR_COMM, "TILE across ranks needs cn_comm_init first");
+        if ((rc = ensure_scratch((size_t)x->global_elems() * esz + 256))) return rc;
+        if ((rc = comm_group_start(&err_))) return rc;
+        for (int p = 0; p < nranks_; ++p) {
+            int64_t b, e;
+            partition(x->shape[0], &b, &e, p);
+            if (e <= b) continue;
+            if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * x->unit * esz, (e - b) * x->unit, dtype, p, stream_, &err_))) return rc;
+        }
+        if ((rc = comm_group_end(&err_))) return rc;
+        src = scratch_;
+    }
+    rc = cuda_fail(launch_tile(out->buf.data, oshape, out->row_begin, out->local_rows(), src, sshape, dtype, stream_), "tile");
+    if (rc) return rc;
+    stats_.kernel_launches++;
+    out->halo_valid = false;
+    return CN_OK;
+}
+
 // Seeded uniform fill (an addition: the reference's random.randn returns zeros,
 // charmnumeric/random.py:4-5).  Element with global linear index g depends on (seed, g)
 // only, so the values do not change with the number of ranks.

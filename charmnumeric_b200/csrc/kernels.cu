@@ -338,6 +338,36 @@ cudaError_t launch_matvec(const void* A, int64_t lda, const void* x, void* y, in
     return cudaGetLastError();
 }
 
+// ---- tile ---------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+__global__ void tile_kernel(T* dst, long long d1, long long d2, long long row0, long long n,
+                            const T* src, long long s0, long long s1, long long s2) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long i2 = i % d2, t = i / d2;
+        const long long i1 = t % d1, i0 = row0 + t / d1;
+        dst[i] = src[((i0 % s0) * s1 + (i1 % s1)) * s2 + (i2 % s2)];
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_tile(void* dst, const int64_t dst_shape[3], int64_t dst_row_begin, int64_t dst_rows,
+                        const void* src, const int64_t src_shape[3], int dtype, cudaStream_t s) {
+    const long long n = (long long)dst_rows * dst_shape[1] * dst_shape[2];
+    if (n <= 0) return cudaSuccess;
+    const int grid = grid_for(n, 256);
+    if (dtype_size(dtype) == 8)
+        tile_kernel<long long><<<grid, 256, 0, s>>>((long long*)dst, dst_shape[1], dst_shape[2], dst_row_begin, n,
+                                                    (const long long*)src, src_shape[0], src_shape[1], src_shape[2]);
+    else
+        tile_kernel<int><<<grid, 256, 0, s>>>((int*)dst, dst_shape[1], dst_shape[2], dst_row_begin, n,
+                                              (const int*)src, src_shape[0], src_shape[1], src_shape[2]);
+    return cudaGetLastError();
+}
+
 // ---- halo exchange over peer mappings ---------------------------------------------------------
 // Phase 1: all blocks store this rank's boundary rows into the neighbours' payload slots; each
 // block fences, then draws a ticket, and the block with the last ticket publishes the payload

@@ -32,6 +32,11 @@ cudaError_t launch_dot(const void* a, const void* b, int64_t n, int dtype, void*
 cudaError_t launch_matvec(const void* A, int64_t lda, const void* x, void* y, int64_t rows,
                           int64_t cols, int dtype, cudaStream_t s);
 
+// TILE (charmnumeric/operations.py:52-72): dst[i0,i1,i2] = src[i0 % s0, i1 % s1, i2 % s2] for
+// the local rows of dst (shapes right-aligned into three dimensions; src is the whole array).
+cudaError_t launch_tile(void* dst, const int64_t dst_shape[3], int64_t dst_row_begin, int64_t dst_rows,
+                        const void* src, const int64_t src_shape[3], int dtype, cudaStream_t s);
+
 // Halo exchange through the peer mailboxes (takes the place of the per-edge messages of
 // src/executor_core.cpp:7-143 and PartitionImpl::receive_data, src/partition_comm.cpp:25-61).
 // Rows are 8-byte multiples; pointers of absent neighbours are null.

@@ -112,7 +112,7 @@ class _Op:
     __slots__ = ("kind", "opcode", "result", "operands", "region", "payload")
 
     def __init__(self, kind, opcode=None, result=None, operands=(), region=None, payload=None):
-        self.kind = kind          # "ew", "set", "create", "reduce", "sum", "matmul", "diag", "randu", "put"
+        self.kind = kind          # "ew", "set", "create", "reduce", "sum", "matmul", "diag", "tile", "randu", "put"
         self.opcode = opcode
         self.result = result      # _Info
         self.operands = list(operands)  # (_Info, Region | None) or python scalar
@@ -491,6 +491,24 @@ def _matvec(mat, vec):
         raise ValueError(f"Shape mismatch: matrix cols {mat.shape[1]} != vector size {vec.shape[0]}")
     out = _new_array((mat.shape[0],), _result_dtype(mat, vec))
     _record(_Op("matmul", wire.OP_MATMUL, out._info, [mat._operand(), vec._operand()]))
+    return out
+
+
+def tile(x, reps):
+    """numpy.tile for backend arrays (charmnumeric/operations.py:52-72)."""
+    if _is_scalar_like(x):
+        return asarray(np.tile(np.asarray(x), reps))
+    x = _whole(asarray(x))
+    reps = (int(reps),) if isinstance(reps, (int, np.integer)) else tuple(int(r) for r in reps)
+    if any(r < 1 for r in reps):
+        raise ValueError("tile: repeat counts must be positive")
+    nd = max(x.ndims, len(reps))
+    if nd > 3:
+        raise NotImplementedError("tile: results with more than three dimensions are outside this backend's scope")
+    shape = (1,) * (nd - x.ndims) + tuple(x.shape)
+    full = (1,) * (nd - len(reps)) + reps
+    out = _new_array(tuple(s * r for s, r in zip(shape, full)), x.dtype)
+    _record(_Op("tile", wire.OP_TILE, out._info, [x._operand()], payload=full))
     return out
 
 
@@ -879,6 +897,10 @@ def _single_node(op):
     elif op.kind in ("reduce", "matmul", "sum"):
         root = wire.Ast(res.name, op.opcode, shape=res.shape, dtype=dt,
                         operands=[(_leaf(i), r) for i, r in op.operands])
+    elif op.kind == "tile":
+        root = wire.Ast(res.name, wire.OP_TILE, shape=res.shape, dtype=dt,
+                        operands=[(_leaf(i), r) for i, r in op.operands]
+                        + [(wire.scalar(float(rep)), None) for rep in op.payload])
     elif op.kind == "diag":
         root = wire.Ast(res.name, wire.OP_DIAG, shape=res.shape, dtype=dt,
                         operands=[(_leaf(i), r) for i, r in op.operands]

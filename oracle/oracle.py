@@ -29,7 +29,7 @@ _LIB = _HERE / "libcn_oracle.so"
 
 OP_COPY, OP_SET_REGION, OP_CREATE, OP_NOOP = -5, -4, -2, -1
 OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MATMUL, OP_TANH, OP_EXP, OP_REDUCE = 0, 1, 2, 3, 4, 5, 6, 8
-OP_DIAG = 10
+OP_TILE, OP_DIAG = 7, 10
 OP_SQRT, OP_ABS, OP_SUM, OP_RANDU = 11, 12, 13, 14
 NP_DTYPES = {0: np.dtype("float32"), 1: np.dtype("float64"), 2: np.dtype("int32"),
              3: np.dtype("int64")}
@@ -255,6 +255,11 @@ class Oracle:
                 else:
                     y = (np.asarray(A) @ np.asarray(x)).astype(dtype)
                 self.arrays[r.result_name] = y.astype(dtype)
+            elif op == OP_TILE:
+                # charmnumeric/operations.py:52-72: numpy.tile with the padded repeat counts
+                v = self.arrays[r.operands[0][0].result_name]
+                reps = tuple(int(o[0].scalar) for o in r.operands[1:])
+                self.arrays[r.result_name] = np.ascontiguousarray(np.tile(v, reps)).astype(dtype)
             elif op == OP_DIAG:
                 # src/execute_node.cpp:600-750: vector -> diagonal matrix, matrix -> k-th diagonal
                 v = self.arrays[r.operands[0][0].result_name]

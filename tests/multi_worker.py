@@ -57,8 +57,14 @@ def main():
         d = cnp.diag(A)
         x = cnp.random.uniform((n,), seed=32)
         return {"A": A, "d": d, "x1": x + (1.0 / d) * (cnp.ones((n,)) - A @ x)}
+
+    def tile():
+        h0 = cnp.random.uniform((37,), seed=41)
+        m = cnp.random.uniform((5, 6), seed=42)
+        return {"rows": cnp.tile(h0, (11, 1)), "blocks": cnp.tile(m, (3, 2)), "cube": cnp.tile(h0, (2, 3, 1))}
     progs["chain"] = chain
     progs["diag"] = diag
+    progs["tile"] = tile
     progs["matvec"] = matvec
     cnp.reset_frontend_state()
     outs = progs[case]()

@@ -55,6 +55,11 @@ def test_diag_through_the_oracle(cpu_interface, n, k):
     G.test_diag_matches_numpy(cpu_interface, n, k)
 
 
+@pytest.mark.parametrize("shape,reps", [((5,), 3), ((7,), (4, 1)), ((3, 4), (2, 3)), ((2, 3, 4), (3, 1, 2))])
+def test_tile_through_the_oracle(cpu_interface, shape, reps):
+    G.test_tile_matches_numpy(cpu_interface, shape, reps)
+
+
 def _dry(prog):
     cnp.reset_frontend_state()
     outs = prog()

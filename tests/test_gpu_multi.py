@@ -40,7 +40,7 @@ def _run_ranks(tmp_path, case, nranks, p2p, overlap=0):
 
 
 def _check(case, results, p2p):
-    exact = case.startswith("jacobi")
+    exact = case.startswith("jacobi") or case == "tile"
     for r, d in enumerate(results):
         for key in d.files:
             if not key.startswith("gpu_"):
@@ -64,7 +64,7 @@ def _check(case, results, p2p):
                     assert d[key].tobytes() == results[0][key].tobytes(), (case, key)
 
 
-@pytest.mark.parametrize("case", ["jacobi2d", "jacobi2d_small", "jacobi3d", "cg", "chain", "matvec", "diag"])
+@pytest.mark.parametrize("case", ["jacobi2d", "jacobi2d_small", "jacobi3d", "cg", "chain", "matvec", "diag", "tile"])
 @pytest.mark.parametrize("nranks", [2, 4])
 def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
     if _gpu_count() < nranks:

@@ -231,6 +231,15 @@ def test_diag_matches_numpy(interface, n, k):
     assert np.array_equal(tall, np.diag(m.T, k))
 
 
+@pytest.mark.parametrize("shape,reps", [((5,), 3), ((7,), (4, 1)), ((3, 4), (2, 3)), ((6,), (2, 3, 2)),
+                                        ((2, 3, 4), (3, 1, 2)), ((1,), (9,))])
+def test_tile_matches_numpy(interface, shape, reps):
+    """TILE (charmnumeric/operations.py:52-72), e.g. tile(h0, (b, 1)) of examples/lstm_forward.py:31."""
+    host = np.arange(1.0, 1.0 + int(np.prod(shape))).reshape(shape)
+    got = cnp.tile(cnp.asarray(host), reps).get(interface)
+    assert np.array_equal(got, np.tile(host, reps))
+
+
 def _cg_poisson_program(m, iters):
     def prog():
         b = cnp.zeros((m, m))
