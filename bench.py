@@ -257,6 +257,12 @@ def run_gpu(args, rank, world, local_rank):
     itf = cnp.CharmNumericInterface(device=local_rank, rank=rank, nranks=world, unique_id=uid)
     ctx = itf.context
     cnp.reset_frontend_state()
+    # halo depth: sweeps without a fused reduction also update the halo rows they can, so a
+    # deeper halo means fewer exchanges (Jacobi2D: one per 8 sweeps; measured no gain for the
+    # 8 MiB planes of Jacobi3D, whose exchange is bandwidth, not latency)
+    halo = args.halo if args.halo > 0 else {"jacobi2d": 8}.get(args.workload, 1)
+    if world > 1:
+        ctx.set_option("halo", halo)
     wl = WORKLOADS[args.workload](itf, nranks=world, scale=args.scale)
     K, W = max(1, args.steps), max(3, args.warmup)
 
@@ -349,6 +355,7 @@ def run_gpu(args, rank, world, local_rank):
             "vs_baseline": None, "dtype": "f64", "data": "synthetic",
             "config": {"workload": wl.description, "l2": "working set far larger than L2; no flush",
                        "parallelism": f"slab{world}", "scale": args.scale,
+                       "halo_depth": halo if world > 1 else 0,
                        "aggregate": ("value = GPUs x iterations/s of the per-GPU slab" if agg > 1
                                      else "value = steps/s of the whole problem")},
             "roofline": roofline,
@@ -386,6 +393,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--scale", type=float, default=1.0, help="linear problem-size factor (1 = the configured size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--halo", type=int, default=0, help="halo rows per side for N > 1 (0: per-workload default)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

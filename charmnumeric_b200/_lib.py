@@ -23,7 +23,7 @@ class CnError(RuntimeError):
 class Stats(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
         "kernel_launches", "group_launches", "compiles", "halo_exchanges", "allreduces",
-        "fused_reductions", "nodes", "bytes_h2d", "bytes_d2h", "plan_hits", "peer_exchanges", "overlapped_sweeps")]
+        "fused_reductions", "nodes", "bytes_h2d", "bytes_d2h", "plan_hits", "peer_exchanges", "overlapped_sweeps", "deep_halo_sweeps")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}

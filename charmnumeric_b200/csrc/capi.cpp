@@ -224,6 +224,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->plan_hits = s.plan_hits;
     out->peer_exchanges = s.peer_exchanges;
     out->overlapped_sweeps = s.overlapped_sweeps;
+    out->deep_halo_sweeps = s.deep_halo_sweeps;
     return cn::CN_OK;
 }
 
@@ -243,6 +244,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         ctx->impl.set_staged_tile(-1, (int)value);
     } else if (k == "debug_drop_copies") {
         ctx->impl.set_debug_drop_copies(value != 0);
+    } else if (k == "deep_halo") {
+        ctx->impl.set_deep_halo(value != 0);
     } else if (k == "overlap_halo") {
         ctx->impl.set_overlap_halo(value != 0);
     } else if (k == "debug_peer_wait") {

@@ -30,6 +30,11 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_FLAT_PREFETCH")) flat_prefetch_ = atoi(f) != 0;
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
     if (const char* f = getenv("CN_OVERLAP_HALO")) overlap_halo_ = atoi(f) != 0;
+    if (const char* f = getenv("CN_DEEP_HALO")) deep_halo_ = atoi(f) != 0;
+    if (const char* f = getenv("CN_HALO")) {
+        int v = atoi(f);
+        if (v >= 0 && v <= 8) halo_ = v;
+    }
     staged_tile_.tx = 64;
     staged_tile_.r = 4;
     if (const char* n = getenv("CN_STAGED_NS")) {
@@ -209,7 +214,7 @@ int Context::create_array(int name, int ndims, const int64_t* shape, int dtype, 
             if (zero) {
                 int rc = cuda_fail(cudaMemsetAsync(old->buf.alloc, 0, old->buf.bytes, stream_), "memset");
                 if (rc) return rc;
-                old->halo_valid = false;
+                old->halo_fresh = 0;
             }
             if (out) *out = old;
             return CN_OK;
@@ -386,7 +391,7 @@ int Context::ensure_second_stream() {
 }
 
 int Context::exchange_halo(Array* a, cudaStream_t st) {
-    if (nranks_ == 1 || a->replicated || a->halo_valid) return CN_OK;
+    if (nranks_ == 1 || a->replicated || (a->halo > 0 && a->halo_fresh == a->halo)) return CN_OK;
     if (!comm_.ready) return fail(CN_ERR_COMM, "halo exchange needs cn_comm_init first");
     const int H = a->halo;
     const int64_t nl = a->local_rows();
@@ -411,7 +416,7 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
         if ((size_t)cnt * esz <= CN_PEER_HALO_SLOT && (cnt * esz) % 8 == 0) {
             if (has_prev || has_next)
                 if ((rc = exchange_halo_p2p(a, has_prev, has_next, st))) return rc;
-            a->halo_valid = true;
+            a->halo_fresh = a->halo;
             stats_.halo_exchanges++;
             return CN_OK;
         }
@@ -428,7 +433,7 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
     }
     if ((rc = comm_group_end(&err_))) return rc;
     prof_stop();
-    a->halo_valid = true;
+    a->halo_fresh = a->halo;
     stats_.halo_exchanges++;
     return CN_OK;
 }
@@ -756,7 +761,7 @@ int Context::try_plain_fill(const DagNode& node, bool* done) {
             if (rc) return rc;
             stats_.kernel_launches++;
         }
-        a->halo_valid = false;
+        a->halo_fresh = 0;
     }
     *done = true;
     return CN_OK;

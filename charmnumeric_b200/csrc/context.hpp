@@ -38,7 +38,7 @@ struct Array {
     int64_t unit = 1;                    // elements per index of dimension 0
     int halo = 0;                        // halo rows allocated on each side
     Buffer buf, shadow;
-    bool halo_valid = false;
+    int halo_fresh = 0;  // halo rows (per side) that hold the neighbours' current values, 0..halo
 
     int64_t local_rows() const { return row_end - row_begin; }
     int64_t local_elems() const { return local_rows() * unit; }
@@ -93,6 +93,7 @@ struct Stats {
     long long plan_hits = 0;         // DAGs served from the plan cache
     long long peer_exchanges = 0;    // reductions finished / halos moved through the peer mailboxes
     long long overlapped_sweeps = 0; // stencil sweeps whose interior ran beside the halo exchange
+    long long deep_halo_sweeps = 0;  // stencil sweeps that also updated halo rows (no exchange needed next)
 };
 
 struct DriverApi {
@@ -165,6 +166,7 @@ public:
     void set_flat_prefetch(bool on) { flat_prefetch_ = on; plans_.clear(); }
     void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
     void set_overlap_halo(bool on) { overlap_halo_ = on; }
+    void set_deep_halo(bool on) { deep_halo_ = on; }
     void set_p2p(bool on) { p2p_wanted_ = on; }  // takes effect at cn_comm_init
     bool p2p_ready() const { return peer_.ready; }
 
@@ -232,6 +234,7 @@ private:
     cudaStream_t stream2_ = nullptr;
     cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
     cudaStream_t prof_stream_ = nullptr;
+    bool deep_halo_ = true;      // with halo > 1: sweeps also update halo rows, fewer exchanges
     bool overlap_halo_ = false;  // measured: no gain at 2048^2, a loss at 1024^3 (the halo kernel's
                                  // blocks queue behind the persistent interior blocks)
     cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;

@@ -348,20 +348,39 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     }
     if (!ref) return fail(CN_ERR_UNSUPPORTED, "group touches no array");
 
-    // halos: a leaf shifted along dimension 0 reads rows owned by a neighbour
+    // halos: a leaf shifted along dimension 0 reads rows owned by a neighbour.  Every array
+    // keeps count of how many of its halo rows still hold the neighbours' current values
+    // (halo_fresh); an exchange refreshes all `halo` rows at once.
     std::vector<Array*> stale;
+    int64_t ext = 0;  // rows beyond each slab edge that this sweep computes redundantly
     if (nranks_ > 1 && !ref->replicated) {
         if (g.max_halo > halo_) return fail(CN_ERR_UNSUPPORTED, "stencil reaches further along dimension 0 than the halo depth");
-        for (auto& l : g.leaves)
-            if (l.delta[0] != 0) {
-                Array* x = find(l.name);
-                if (!x->halo_valid && std::find(stale.begin(), stale.end(), x) == stale.end()) stale.push_back(x);
+        std::vector<int64_t> reach(ins.size(), 0);  // how far each input is read along dimension 0
+        for (auto& l : g.leaves) {
+            const int64_t r = l.delta[0] < 0 ? -l.delta[0] : l.delta[0];
+            for (size_t i = 0; i < in_names.size(); ++i)
+                if (in_names[i] == l.name) reach[i] = std::max(reach[i], r);
+        }
+        for (size_t i = 0; i < ins.size(); ++i)
+            if (reach[i] > 0 && ins[i]->halo_fresh < reach[i]) stale.push_back(ins[i]);
+        // With a halo deeper than the stencil's reach a sweep can also update rows of the halo
+        // itself (the neighbour computes the same values for its own rows), so that the next
+        // sweeps need no exchange: one exchange of `halo` rows serves up to halo / reach sweeps.
+        if (deep_halo_ && halo_ > 1 && g.reds.empty() && g.souts.empty() && !g.flat && ref->row_end > ref->row_begin) {
+            int64_t e = halo_;
+            for (size_t i = 0; i < ins.size(); ++i) {
+                const bool refreshed = std::find(stale.begin(), stale.end(), ins[i]) != stale.end();
+                const int64_t fresh = refreshed ? ins[i]->halo : ins[i]->halo_fresh;
+                e = std::min<int64_t>(e, std::min<int64_t>(fresh, ins[i]->halo) - reach[i]);
             }
+            for (Array* x : outs) e = std::min<int64_t>(e, x->halo);
+            ext = std::max<int64_t>(e, 0);
+        }
     }
     // Without a fused reduction the sweep can be cut along dimension 0: the rows next to the
     // slab edges wait for the neighbours' halo rows on a second stream while the interior,
     // which needs none of them, runs on the main stream.
-    const bool overlap = overlap_halo_ && !stale.empty() && g.reds.empty() && g.souts.empty() && !g.flat;
+    const bool overlap = overlap_halo_ && !stale.empty() && g.reds.empty() && g.souts.empty() && !g.flat && ext == 0;
     if (!overlap)
         for (Array* x : stale)
             if ((rc = exchange_halo(x, stream_))) return rc;
@@ -387,10 +406,13 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         rlo[d] = g.reg_lo[d];
         rhi[d] = g.reg_hi[d];
     }
-    lo[0] = std::max(lo[0], rb) - rb;
-    hi[0] = std::min(hi[0], re) - rb;
-    rlo[0] = std::max(rlo[0], rb) - rb;
-    rhi[0] = std::min(rhi[0], re) - rb;
+    // local rows, widened by `ext` towards every neighbour that exists (the global box clips at
+    // the physical edges of the array by itself)
+    const int64_t wb = rb - (rb > 0 ? ext : 0), we = re + (re < ref->shape[0] ? ext : 0);
+    lo[0] = std::max(lo[0], wb) - rb;
+    hi[0] = std::min(hi[0], we) - rb;
+    rlo[0] = std::max(rlo[0], wb) - rb;
+    rhi[0] = std::min(rhi[0], we) - rb;
     int64_t strides[3];
     array_strides(*ref, strides);
     const int V = g.vec;
@@ -561,8 +583,9 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     for (size_t m = 0; m < outs.size(); ++m) {
         Array* x = outs[m];
         if (g.copy_through && g.outs[m].hazard) std::swap(x->buf, x->shadow);
-        x->halo_valid = false;
+        x->halo_fresh = (int)ext;  // the widened sweep left that many halo rows up to date
     }
+    if (ext > 0) stats_.deep_halo_sweeps++;
     for (auto& sw : swaps) {
         free_buffer(&sw.first->buf);
         sw.first->buf = sw.second;
@@ -670,7 +693,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
             a.out[m] = x->buf.data;
             bind_view(*x, o.region, &a.out_off[m], a.out_str[m]);
         }
-        x->halo_valid = false;
+        x->halo_fresh = 0;
     }
     for (int d = 0; d < 3; ++d) a.ext[d] = d < nd ? ext[d] : 1;
     int64_t total = 1;
@@ -805,7 +828,7 @@ int Context::execute_matmul(const AstNode& r) {
         prof_stop();
         if (rc) return rc;
         stats_.kernel_launches++;
-        y->halo_valid = false;
+        y->halo_fresh = 0;
         return CN_OK;
     }
     // multi-rank: whole operands only, so that A's and y's row partitions coincide
@@ -827,7 +850,7 @@ int Context::execute_matmul(const AstNode& r) {
     prof_stop();
     if (rc) return rc;
     stats_.kernel_launches++;
-    y->halo_valid = false;
+    y->halo_fresh = 0;
     return CN_OK;
 }
 
@@ -886,7 +909,7 @@ int Context::execute_diag(const AstNode& r) {
         if (rc) return rc;
         stats_.kernel_launches++;
     }
-    out->halo_valid = false;
+    out->halo_fresh = 0;
     return CN_OK;
 }
 
@@ -942,7 +965,7 @@ int Context::execute_tile(const AstNode& r) {
     rc = cuda_fail(launch_tile(out->buf.data, oshape, out->row_begin, out->local_rows(), src, sshape, dtype, stream_), "tile");
     if (rc) return rc;
     stats_.kernel_launches++;
-    out->halo_valid = false;
+    out->halo_fresh = 0;
     return CN_OK;
 }
 
@@ -965,7 +988,7 @@ int Context::execute_randu(const AstNode& r) {
                                 (uint64_t)v[0], v[1], v[2], stream_), "randu");
     if (rc) return rc;
     stats_.kernel_launches++;
-    x->halo_valid = false;
+    x->halo_fresh = 0;
     return CN_OK;
 }
 
@@ -1055,7 +1078,7 @@ int Context::put(int name, int ndims, const int64_t* shape, int dtype, const voi
         if ((rc = cuda_fail(cudaMemcpyAsync(x->buf.data, src, bytes, cudaMemcpyHostToDevice, stream_), "put copy"))) return rc;
         stats_.bytes_h2d += bytes;
     }
-    x->halo_valid = false;
+    x->halo_fresh = 0;
     return CN_OK;
 }
 

@@ -167,10 +167,14 @@ typedef struct cn_stats {
     int64_t plan_hits;         /* DAGs whose bytes had run before (parsing and lowering skipped) */
     int64_t peer_exchanges;    /* reductions finished in-kernel / halos moved through peer mailboxes */
     int64_t overlapped_sweeps; /* stencil sweeps whose interior ran beside the halo exchange */
+    int64_t deep_halo_sweeps;  /* stencil sweeps that also updated halo rows (see option "halo") */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
-/* Options: "halo" depth (rows per side, default 1; set before creating arrays),
+/* Options: "halo" depth (rows per side, 0..8, default 1; set before creating arrays; with a depth
+ * above the stencil's reach, sweeps without a fused reduction also update the halo rows they can
+ * (the neighbour computes the same values), so one exchange serves several sweeps; "deep_halo" 0
+ * switches that off),
  * "fuse_reductions" 0/1, "tile_tx" / "tile_rows" (shape of generated kernels: threads along
  * the last dimension, rows per thread), "staged" 0/1/2 (TMA / shared-memory staging of stencil
  * tiles: never / 3-D groups only (default) / 2-D groups too; process-wide), "staged_tile_tx" /

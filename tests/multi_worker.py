@@ -36,6 +36,8 @@ def main():
     progs = {
         "jacobi2d": G._jacobi2d_program(67, 130, 6, res_every=3),
         "jacobi2d_small": G._jacobi2d_program(9, 8, 3),
+        "jacobi2d_long": G._jacobi2d_program(67, 130, 23, res_every=5),
+        "jacobi3d_long": G._jacobi3d_program((26, 12, 34), 9),
         "jacobi3d": G._jacobi3d_program((19, 12, 34), 3),
         "cg": G._cg_poisson_program(34, 8),
     }
@@ -79,6 +81,7 @@ def main():
     result["allreduces"] = np.array(st["allreduces"])
     result["peer_exchanges"] = np.array(st["peer_exchanges"])
     result["overlapped_sweeps"] = np.array(st["overlapped_sweeps"])
+    result["deep_halo_sweeps"] = np.array(st["deep_halo_sweeps"])
     np.savez(os.path.join(outdir, f"{case}_rank{rank}.npz"), **result)
     itf.close()
 

@@ -19,9 +19,9 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-def _run_ranks(tmp_path, case, nranks, p2p, overlap=0):
+def _run_ranks(tmp_path, case, nranks, p2p, overlap=0, halo=1):
     idfile = str(tmp_path / "nccl_id")
-    env = dict(os.environ, CN_P2P=str(p2p), CN_OVERLAP_HALO=str(overlap))
+    env = dict(os.environ, CN_P2P=str(p2p), CN_OVERLAP_HALO=str(overlap), CN_HALO=str(halo))
     procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "multi_worker.py"), str(r), str(nranks),
                                idfile, str(tmp_path), case], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                               text=True, env=env) for r in range(nranks)]
@@ -90,3 +90,21 @@ def test_multi_gpu_overlapped_halo(tmp_path, case):
     _check(case, results, 1)
     for d in results:
         assert int(d["overlapped_sweeps"]) > 0
+
+
+@pytest.mark.parametrize("case,halo,p2p,nranks", [
+    ("jacobi2d_long", 4, 1, 2), ("jacobi2d_long", 3, 0, 2), ("jacobi3d_long", 4, 1, 2), ("cg", 4, 1, 2),
+    ("jacobi2d_long", 4, 1, 4), ("jacobi3d_long", 2, 1, 4)])
+def test_multi_gpu_deep_halo(tmp_path, case, halo, p2p, nranks):
+    """Halo depth above the stencil's reach: sweeps also update halo rows (redundantly with the
+    neighbour), so one exchange serves several sweeps.  Results stay bit-exact."""
+    if _gpu_count() < nranks:
+        pytest.skip(f"needs {nranks} GPUs")
+    results = _run_ranks(tmp_path, case, nranks, p2p, halo=halo)
+    _check(case.replace("_long", ""), results, p2p)
+    for d in results:
+        if case != "cg":
+            sweeps = int(d["deep_halo_sweeps"])
+            assert sweeps > 0
+            # far fewer exchanges than sweeps
+            assert int(d["halo_exchanges"]) < sweeps
