@@ -354,7 +354,8 @@ int Context::setup_peer_boxes() {
     if (!peer_.ready) {
         for (int p = 0; p < nranks_; ++p)
             if (p != rank_ && peer_.box[p]) cudaIpcCloseMemHandle(peer_.box[p]);
-        if (peer_.mine) cudaFree(peer_.mine);
+        // another rank may have mapped this rank's mailbox before the vote failed; freeing
+        // exported memory under a live mapping is undefined, so it stays until the process ends
         if (peer_.ticket) cudaFree(peer_.ticket);
         peer_ = PeerState();
     }
