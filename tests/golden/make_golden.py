@@ -3,7 +3,7 @@
 The reference ships no golden files and cannot be imported or built in this environment
 (charmtyles, Charm++, MLIR and Eigen are absent), so the fixtures hold what the reference's
 own tests compare against -- the NumPy value of each test expression
-(tests/test_backend_integration.py:13-105, examples/cg.py:65-73, examples/matvec.py:45-55) --
+(tests/test_backend_integration.py:13-127, examples/cg.py:65-73, examples/matvec.py:45-55) --
 plus known answers of the seeded generator computed by an independent pure-Python
 implementation.  Run:  python tests/golden/make_golden.py
 """
@@ -47,6 +47,9 @@ def main():
     kats["cg_solution"] = np.linalg.solve(A, b)
     M = 48
     kats["matvec_ipj"] = np.add.outer(np.arange(M, dtype=np.float64), np.arange(M, dtype=np.float64)) @ np.ones(M)
+    for k in (0, 1, -1):  # tests/test_backend_integration.py:108-116
+        kats[f"diag_vector_k{k}"] = np.diag(np.full(8, 2.0), k=k)
+    kats["diag_matrix_k2"] = np.diag(np.full((6, 10), 3.0), k=2)  # :119-127
     np.savez(HERE / "reference_kats.npz", **kats)
 
 

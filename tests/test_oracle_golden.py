@@ -1,6 +1,6 @@
 """CPU-only: the oracle against the committed golden vectors (tests/golden/reference_kats.npz,
 made by tests/golden/make_golden.py from the expressions the reference's own tests and examples
-check against: tests/test_backend_integration.py:13-105, examples/cg.py:65-73,
+check against: tests/test_backend_integration.py:13-127, examples/cg.py:65-73,
 examples/matvec.py:45-55)."""
 from pathlib import Path
 
@@ -81,3 +81,18 @@ def test_matvec_i_plus_j(itf):
     A = cnp.asarray(np.add.outer(np.arange(M, dtype=np.float64), np.arange(M, dtype=np.float64)))
     x = cnp.ones((M,), dtype=np.float64)
     assert np.allclose(A.matvec(x).get(itf), GOLDEN["matvec_ipj"])
+
+
+@pytest.mark.parametrize("k", [0, 1, -1])
+def test_diag_vector(itf, k):
+    """tests/test_backend_integration.py:108-116."""
+    vector = cnp.create_array((8,), dtype=np.float64)
+    vector[:] = 2.0
+    assert np.array_equal(cnp.diag(vector, k=k).get(itf), GOLDEN[f"diag_vector_k{k}"])
+
+
+def test_diag_matrix_extract(itf):
+    """tests/test_backend_integration.py:119-127."""
+    matrix = cnp.create_array((6, 10), dtype=np.float64)
+    matrix[:, :] = 3.0
+    assert np.array_equal(cnp.diag(matrix, k=2).get(itf), GOLDEN["diag_matrix_k2"])
