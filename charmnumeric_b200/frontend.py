@@ -750,6 +750,23 @@ class CharmNumericInterface:
     def close(self):
         self.context.close()
 
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        self.close()
+
+
+class LocalCluster(CharmNumericInterface):
+    """Source-compatible stand-in for the reference's LocalCluster
+    (charmnumeric/interface.py:26-129), which starts a ``charmrun`` server and connects to it.
+    There is no server process here: the backend lives in this process, so the launcher's
+    arguments (server binary, port, odf, PE count ...) are accepted and ignored, and the object
+    is simply the interface of GPU ``device``, usable as a context manager."""
+
+    def __init__(self, server_binary=None, *, device=0, **_launcher_options):
+        super().__init__(device=device)
+
 
 # ---- DAG building -------------------------------------------------------------------------------------
 
