@@ -806,7 +806,9 @@ int Context::execute_matmul(const AstNode& r) {
     if (rc) return rc;
     if ((rc = operand_array(r.operands[1], &x, &rx))) return rc;
     if (A->ndims != 2) return fail(CN_ERR_UNSUPPORTED, "only 2-D matrices are supported by matvec (3-D dim-drop and mat-mat are out of scope)");
-    if (x->ndims != 1) return fail(CN_ERR_UNSUPPORTED, "matvec needs a 1-D vector");
+    // an (n, 1) column vector is stored and partitioned exactly like a 1-D vector of n
+    const bool column = x->ndims == 2 && x->shape[1] == 1;
+    if (x->ndims != 1 && !column) return fail(CN_ERR_UNSUPPORTED, "matvec needs a 1-D vector or an (n, 1) column");
     if (A->dtype != x->dtype) return fail(CN_ERR_BAD_DTYPE, "matvec operands have different dtypes");
     if (!ra.unit_step() || !rx.unit_step()) return fail(CN_ERR_UNSUPPORTED, "matvec on stepped views is not supported");
     const int64_t rows = ra.extent(0), cols = ra.extent(1);
@@ -814,10 +816,10 @@ int Context::execute_matmul(const AstNode& r) {
     const size_t esz = dtype_size(A->dtype);
     const int dtype = A->dtype;
     const int aname = A->name, xname = x->name;
-    int64_t yshape[1] = {rows};
+    int64_t yshape[2] = {rows, 1};
     Array* y = nullptr;
     if (r.result_name == aname || r.result_name == xname) return fail(CN_ERR_HAZARD, "matvec result aliases an operand");
-    if ((rc = create_array(r.result_name, 1, yshape, dtype, false, &y))) return rc;
+    if ((rc = create_array(r.result_name, column ? 2 : 1, yshape, dtype, false, &y))) return rc;
     A = find(aname);
     x = find(xname);
     if (nranks_ == 1) {

@@ -483,13 +483,13 @@ def _matmul(a, b):
 def _matvec(mat, vec):
     if not isinstance(vec, _ArrayOps):
         raise ValueError("matvec requires an Array vector")
-    if vec.ndims == 2 and vec.shape[1] == 1:
-        raise NotImplementedError("column-vector matvec is outside this backend's scope")
-    if mat.ndims != 2 or vec.ndims != 1:
-        raise ValueError("matvec requires a 2D matrix and a 1D vector")
+    # a column vector (n, 1) has the memory layout and the partition of a 1-D vector of n
+    column = vec.ndims == 2 and vec.shape[1] == 1
+    if mat.ndims != 2 or not (vec.ndims == 1 or column):
+        raise ValueError("matvec requires a 2D matrix and a 1D vector (or an (n, 1) column)")
     if mat.shape[1] != vec.shape[0]:
         raise ValueError(f"Shape mismatch: matrix cols {mat.shape[1]} != vector size {vec.shape[0]}")
-    out = _new_array((mat.shape[0],), _result_dtype(mat, vec))
+    out = _new_array((mat.shape[0], 1) if column else (mat.shape[0],), _result_dtype(mat, vec))
     _record(_Op("matmul", wire.OP_MATMUL, out._info, [mat._operand(), vec._operand()]))
     return out
 

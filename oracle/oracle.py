@@ -250,11 +250,14 @@ class Oracle:
                 A = A[_slices(r.operands[0][1], A.shape)]
                 x = self.arrays[r.operands[1][0].result_name]
                 x = x[_slices(r.operands[1][1], x.shape)]
+                column = x.ndim == 2  # (n, 1) column vector: same values, result (m, 1)
+                x = np.ascontiguousarray(x).reshape(-1)
                 if dtype == np.float64:
                     y = gemv(A, x, ref_tile(A.shape[1], 2))
                 else:
                     y = (np.asarray(A) @ np.asarray(x)).astype(dtype)
-                self.arrays[r.result_name] = y.astype(dtype)
+                y = y.astype(dtype)
+                self.arrays[r.result_name] = y.reshape(-1, 1) if column else y
             elif op == OP_TILE:
                 # charmnumeric/operations.py:52-72: numpy.tile with the padded repeat counts
                 v = self.arrays[r.operands[0][0].result_name]

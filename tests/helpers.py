@@ -81,5 +81,8 @@ class OracleInterface:
     def get(self, ndims, name, size, dtype=None):
         return np.array(self.mirror.get(name)).reshape(-1)
 
+    def connect(self, *args, **kwargs):
+        return self
+
     def close(self):
         pass

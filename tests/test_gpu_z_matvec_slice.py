@@ -24,3 +24,14 @@ def test_matvec_on_slices(interface, rows, cols):
     want = A_np[r0:r1, c0:c1] @ x_np[c0:c1]
     assert got.shape == want.shape
     assert np.max(np.abs(got - want)) <= 1e-10 * np.max(np.abs(want))
+
+
+def test_matvec_with_a_column_vector(interface):
+    """examples/matvec.py:30-34 (default mode): the vector is an (n, 1) column, the result (m, 1)."""
+    rng = np.random.default_rng(11)
+    A_np = rng.uniform(-1.0, 1.0, (48, 64))
+    x_np = rng.uniform(-1.0, 1.0, (64, 1))
+    got = cnp.asarray(A_np).matvec(cnp.asarray(x_np)).get(interface)
+    want = A_np @ x_np
+    assert got.shape == (48, 1)
+    assert np.max(np.abs(got - want)) <= 1e-10 * np.max(np.abs(want))
