@@ -56,3 +56,17 @@ def test_reference_example_runs_unmodified(program, args, expect):
     assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
     if expect:
         assert expect in res.stdout, res.stdout[-1500:]
+
+
+@pytest.mark.skipif(not (REFERENCE / "tests" / "test_backend_integration.py").is_file(),
+                    reason="no checkout of the reference next to this repository")
+def test_reference_integration_suite_runs_unmodified(tmp_path):
+    """The reference's tests/test_backend_integration.py as it stands (its conftest, which starts
+    a charmrun server, is left out; tests/reference_suite_plugin.py supplies the two fixtures)."""
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([str(ROOT), str(ROOT / "charmnumeric_b200" / "compat")])
+    res = subprocess.run([sys.executable, "-m", "pytest", "--noconftest", "-p", "tests.reference_suite_plugin",
+                          "-p", "no:cacheprovider", "-q", str(REFERENCE / "tests" / "test_backend_integration.py")],
+                         capture_output=True, text=True, timeout=600, cwd=str(tmp_path), env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-1500:]
+    assert " passed" in res.stdout and "failed" not in res.stdout
