@@ -66,6 +66,11 @@ struct Reader {
         if (ok && err) *err = m;
         ok = false;
     }
+    // A count read from the blob can never exceed what the bytes that are left could hold:
+    // checked before anything is sized by it, so a few bytes cannot ask for gigabytes.
+    bool fits(int64_t count, size_t min_bytes_each) const {
+        return count >= 0 && (uint64_t)count <= (uint64_t)(end - p) / min_bytes_each;
+    }
 };
 
 void read_region(Reader& r, Region* out) {
@@ -143,7 +148,7 @@ void read_node(Reader& r, DagNode* node) {
     node->fusible = r.i32() != 0;
     int ndeps = r.i32();
     if (!r.ok) return;
-    if (ndeps < 0 || ndeps > 1 << 20) {
+    if (ndeps < 0 || ndeps > 1 << 20 || !r.fits(ndeps, 4)) {
         r.fail("dependency count out of range");
         return;
     }
@@ -151,7 +156,7 @@ void read_node(Reader& r, DagNode* node) {
     for (int i = 0; i < ndeps; ++i) node->deps[i] = r.i32();
     int nroots = r.i32();
     if (!r.ok) return;
-    if (nroots < 0 || nroots > 4096) {
+    if (nroots < 0 || nroots > 4096 || !r.fits(nroots, 36)) {  // an ast is at least 36 bytes
         r.fail("root count out of range");
         return;
     }
@@ -172,11 +177,11 @@ int parse_dag(const char* msg, int64_t size, Dag* out, std::string* err) {
     Reader r{msg + 4, msg + size, err};
     out->epoch = r.i32();
     int n = r.i32();
-    if (r.ok && (n < 0 || n > 1 << 22)) r.fail("node count out of range");
+    if (r.ok && (n < 0 || n > 1 << 22 || !r.fits(n, 24))) r.fail("node count out of range");  // a node is at least 24 bytes
     if (r.ok) out->nodes.resize(n);
     for (int i = 0; i < n && r.ok; ++i) read_node(r, &out->nodes[i]);
     int nd = r.i32();
-    if (r.ok && (nd < 0 || nd > 1 << 24)) r.fail("delete count out of range");
+    if (r.ok && (nd < 0 || nd > 1 << 24 || !r.fits(nd, 4))) r.fail("delete count out of range");
     for (int i = 0; i < nd && r.ok; ++i) out->deletes.push_back(r.i32());
     if (r.ok && r.p != r.end) r.fail("trailing bytes after DAG blob");
     return r.ok ? CN_OK : CN_ERR_BAD_BLOB;
