@@ -48,6 +48,22 @@ class DType:
             raise TypeError(f"Unsupported wire dtype {code!r}")
         return NP_DTYPES[code]
 
+    @staticmethod
+    def promote(a, b):
+        """Promoted wire dtype of two wire dtypes (charmnumeric.py:71-75)."""
+        return DType.from_numpy(np.result_type(DType.to_numpy(a), DType.to_numpy(b)))
+
+
+class _CallableInt(int):
+    """An int that can also be called: the reference keeps ``obj.size()`` working next to
+    ``obj.size`` (charmnumeric.py:24-31)."""
+
+    def __new__(cls, value):
+        return int.__new__(cls, int(value))
+
+    def __call__(self):
+        return int(self)
+
 
 def _normalize_dtype(dtype):
     if dtype is None:
@@ -243,7 +259,7 @@ class _ArrayOps:
 
     @property
     def size(self):
-        return _size(self.shape)
+        return _CallableInt(_size(self.shape))
 
     @property
     def itemsize(self):
