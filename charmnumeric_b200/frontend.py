@@ -827,6 +827,10 @@ def _can_join(g, op):
     for info, region in _op_views(op):
         if info.name in g.filled:
             return False
+        # a value computed inside the group is handed on element by element (a register of
+        # the fused kernel): a part of it, or a shifted view of it, has to come from memory
+        if info.name in g.produced and region is not None and region != _full_region(info.shape):
+            return False
         if info.name in g.written and not _is_size1(info):
             dest = g.written[info.name]
             reg = region if region is not None else _full_region(info.shape)

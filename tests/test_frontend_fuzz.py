@@ -1,0 +1,140 @@
+"""Differential test of the lazy frontend (CPU only): seeded random programs -- elementwise
+arithmetic on arrays, views and scalars, shifted and strided slices, in-place region updates
+that read what they overwrite, reductions -- are executed eagerly with NumPy and lazily through
+the frontend (grouping, temporaries, hazards, wire nodes) and the oracle interpreter; every
+array must come out bit-identical.  A share of the programs also goes through the backend's
+host-side compiler, so every group the frontend forms is one the DAG-group compiler accepts.
+
+Only IEEE-exact operations are used (+, -, *, /, abs, sqrt): NumPy is then an exact oracle for
+the oracle."""
+import random
+
+import numpy as np
+import pytest
+
+import charmnumeric_b200 as cnp
+from tests.helpers import OracleInterface
+
+SHAPE = (13, 18)
+
+
+def _random_view(rng, shape):
+    """A pair of slices selecting a sub-box; the result extents are returned too."""
+    sl, ext = [], []
+    for n in shape:
+        step = rng.choice([1, 1, 1, 2])
+        lo = rng.randrange(0, 3)
+        hi = n - rng.randrange(0, 3)
+        sl.append(slice(lo, hi, step))
+        ext.append(len(range(lo, hi, step)))
+    return tuple(sl), tuple(ext)
+
+
+def _same_extent_view(rng, shape, ext, step_ok=True):
+    """Slices of the given extents, shifted at random (as the arms of a stencil are)."""
+    sl = []
+    for n, e in zip(shape, ext):
+        step = rng.choice([1, 1, 2]) if step_ok else 1
+        span = (e - 1) * step + 1
+        if span > n:
+            step, span = 1, e
+        lo = rng.randrange(0, n - span + 1)
+        sl.append(slice(lo, lo + span, step))
+    return tuple(sl)
+
+
+class _Pair:
+    """The same value held eagerly (NumPy) and lazily (frontend)."""
+
+    def __init__(self, eager, lazy):
+        self.e, self.l = eager, lazy
+
+
+def _operand(rng, arrays, ext):
+    kind = rng.random()
+    if kind < 0.2:
+        v = rng.choice([0.5, 2.0, -1.25, 3.0])
+        return _Pair(v, v)
+    a = rng.choice(arrays)
+    sl = _same_extent_view(rng, SHAPE, ext)
+    return _Pair(a.e[sl], a.l[sl])
+
+
+def _expression(rng, arrays, ext, depth):
+    if depth == 0 or rng.random() < 0.25:
+        x = _operand(rng, arrays, ext)
+        if isinstance(x.e, float):          # keep at least one array in every expression
+            y = _operand(rng, arrays, ext)
+            while isinstance(y.e, float):
+                y = _operand(rng, arrays, ext)
+            return _Pair(x.e + y.e, x.l + y.l)
+        return x
+    op = rng.choice(["+", "-", "*", "/", "abs", "sqrt", "neg"])
+    a = _expression(rng, arrays, ext, depth - 1)
+    if op == "abs":
+        return _Pair(np.abs(a.e), cnp.abs(a.l))
+    if op == "sqrt":
+        return _Pair(np.sqrt(np.abs(a.e)), cnp.sqrt(cnp.abs(a.l)))
+    if op == "neg":
+        return _Pair(a.e * -1, -a.l)      # the reference's negation is a multiplication by -1
+    b = _expression(rng, arrays, ext, depth - 1)
+    if op == "+":
+        return _Pair(a.e + b.e, a.l + b.l)
+    if op == "-":
+        return _Pair(a.e - b.e, a.l - b.l)
+    if op == "*":
+        return _Pair(a.e * b.e, a.l * b.l)
+    # keep denominators away from zero so that no NaN / inf comparisons are needed
+    return _Pair(a.e / (np.abs(b.e) + 1.0), a.l / (cnp.abs(b.l) + 1.0))
+
+
+def _program(seed, interface):
+    rng = random.Random(seed)
+    nprng = np.random.default_rng(seed)
+    arrays, scalars = [], []
+    for _ in range(3):
+        host = nprng.uniform(-2.0, 2.0, SHAPE)
+        arrays.append(_Pair(host.copy(), cnp.asarray(host)))
+    for _ in range(rng.randrange(4, 9)):
+        action = rng.random()
+        if action < 0.55:                     # region update, possibly reading what it overwrites
+            target = rng.choice(arrays)
+            dst, ext = _random_view(rng, SHAPE)
+            rhs = _expression(rng, arrays, ext, rng.randrange(1, 4))
+            value = np.array(rhs.e, copy=True)   # the right-hand side is evaluated before the write
+            target.e[dst] = value
+            target.l[dst] = rhs.l
+        elif action < 0.75:                   # a new whole array from an expression
+            rhs = _expression(rng, arrays, SHAPE, rng.randrange(1, 4))
+            lazy = rhs.l.copy() if isinstance(rhs.l, cnp.ArrayView) else rhs.l   # a bare view aliases its base
+            arrays.append(_Pair(np.array(rhs.e, copy=True), lazy))
+        elif action < 0.9:                    # literal fill of a region
+            target = rng.choice(arrays)
+            dst, _ = _random_view(rng, SHAPE)
+            v = rng.choice([0.0, 1.0, -3.5])
+            target.e[dst] = v
+            target.l[dst] = v
+        else:                                 # reduction of a fresh expression
+            rhs = _expression(rng, arrays, SHAPE, 2)
+            scalars.append(_Pair(float(np.sum(rhs.e)), cnp.sum(rhs.l)))
+    for a in arrays:
+        got = a.l.get(interface)
+        assert got.shape == a.e.shape
+        assert got.tobytes() == np.ascontiguousarray(a.e).tobytes(), f"seed {seed}: array differs"
+    for s in scalars:
+        got = float(s.l.get(interface)[0])
+        assert abs(got - s.e) <= 1e-10 * max(1.0, abs(s.e)), f"seed {seed}: reduction differs"
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_random_programs_match_numpy(seed):
+    cnp.reset_frontend_state()
+    _program(seed, OracleInterface(dry_run=False))
+
+
+@pytest.mark.parametrize("seed", range(1000, 1012))
+def test_random_programs_lower_and_compile(seed):
+    cnp.reset_frontend_state()
+    itf = OracleInterface(dry_run=True)      # every fusible group goes through lower + NVRTC
+    _program(seed, itf)
+    assert itf.mirror.compiled > 0
