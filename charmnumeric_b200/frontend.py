@@ -847,16 +847,8 @@ def _can_join(g, op):
     shape = _op_shape(op)
     if g.shape is None or shape == g.shape:
         return True
-    # a whole-array op may follow region updates of same-shaped arrays (fused residuals)
-    if g.uniform and g.array_shape is not None and shape == g.array_shape:
-        for info, region in _op_views(op):
-            if _is_size1(info):
-                continue
-            if info.name in g.produced:
-                return False
-            if info.shape != g.array_shape or (region is not None and region != _full_region(info.shape)):
-                return False
-        return op.kind != "set" or op.region == _full_region(op.result.shape)
+    # ops of another shape start a new group: the backend's kernels iterate over one shape
+    # (reductions over whole arrays are folded into a region group by the backend itself)
     return False
 
 
