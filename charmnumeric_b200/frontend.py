@@ -986,6 +986,10 @@ def build_nodes(ops):
         for op in seg_ops:
             for info, _ in _op_views(op):
                 readers.setdefault(info.name, set()).add(si)
+            if op.kind == "set":
+                # the target of an assignment has to exist as an array, even when the program
+                # drops its last handle on it before the batch is built
+                readers.setdefault(op.result.name, set()).add(si)
     out = []
     for si, (kind, item) in enumerate(segments):
         if kind == "group":

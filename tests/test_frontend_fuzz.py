@@ -50,34 +50,37 @@ class _Pair:
         self.e, self.l = eager, lazy
 
 
-def _operand(rng, arrays, ext, SHAPE):
+def _operand(rng, arrays, ext, SHAPE, device_scalars=()):
     kind = rng.random()
     if kind < 0.2:
         v = rng.choice([0.5, 2.0, -1.25, 3.0])
         return _Pair(v, v)
+    if kind < 0.3 and device_scalars:
+        # a size-1 device array (the alpha and beta of a CG iteration): broadcast like a scalar
+        return rng.choice(device_scalars)
     a = rng.choice(arrays)
     sl = _same_extent_view(rng, SHAPE, ext)
     return _Pair(a.e[sl], a.l[sl])
 
 
-def _expression(rng, arrays, ext, depth, SHAPE):
+def _expression(rng, arrays, ext, depth, SHAPE, device_scalars=()):
     if depth == 0 or rng.random() < 0.25:
-        x = _operand(rng, arrays, ext, SHAPE)
-        if isinstance(x.e, float):          # keep at least one array in every expression
+        x = _operand(rng, arrays, ext, SHAPE, device_scalars)
+        if not isinstance(x.e, np.ndarray):  # keep at least one array in every expression
             y = _operand(rng, arrays, ext, SHAPE)
-            while isinstance(y.e, float):
+            while not isinstance(y.e, np.ndarray):
                 y = _operand(rng, arrays, ext, SHAPE)
             return _Pair(x.e + y.e, x.l + y.l)
         return x
     op = rng.choice(["+", "-", "*", "/", "abs", "sqrt", "neg"])
-    a = _expression(rng, arrays, ext, depth - 1, SHAPE)
+    a = _expression(rng, arrays, ext, depth - 1, SHAPE, device_scalars)
     if op == "abs":
         return _Pair(np.abs(a.e), cnp.abs(a.l))
     if op == "sqrt":
         return _Pair(np.sqrt(np.abs(a.e)), cnp.sqrt(cnp.abs(a.l)))
     if op == "neg":
         return _Pair(a.e * -1, -a.l)      # the reference's negation is a multiplication by -1
-    b = _expression(rng, arrays, ext, depth - 1, SHAPE)
+    b = _expression(rng, arrays, ext, depth - 1, SHAPE, device_scalars)
     if op == "+":
         return _Pair(a.e + b.e, a.l + b.l)
     if op == "-":
@@ -97,17 +100,33 @@ def _program(seed, interface, SHAPE=None):
     for _ in range(3):
         host = nprng.uniform(-2.0, 2.0, SHAPE).astype(dtype)
         arrays.append(_Pair(host.copy(), cnp.asarray(host)))
+    # an array of exactly representable values: its sums and dot products are exact in any order,
+    # so that scalars derived from them can flow back into array expressions bit for bit
+    exact_host = nprng.choice(np.array([-1.0, 0.5, 2.0, 0.25], dtype=dtype), SHAPE)
+    exact = _Pair(exact_host.copy(), cnp.asarray(exact_host))
+    device_scalars = []
     for _ in range(rng.randrange(4, 9)):
+        if rng.random() < 0.25:
+            if rng.random() < 0.5:
+                device_scalars.append(_Pair(dtype(np.sum(exact.e)), cnp.sum(exact.l)))
+            else:
+                device_scalars.append(_Pair(dtype(np.sum(exact.e * exact.e)), cnp.dot2d(exact.l, exact.l)))
+            if len(device_scalars) >= 2 and rng.random() < 0.5:   # scalar-scalar arithmetic on the device
+                a, b = device_scalars[-2], device_scalars[-1]
+                device_scalars.append(_Pair(dtype(a.e / (abs(b.e) + dtype(1.0))), a.l / (cnp.abs(b.l) + 1.0)))
+        if len(arrays) > 3 and rng.random() < 0.2:
+            # drop an array: results nobody holds any more become temporaries of their group
+            del arrays[rng.randrange(len(arrays))]
         action = rng.random()
         if action < 0.55:                     # region update, possibly reading what it overwrites
             target = rng.choice(arrays)
             dst, ext = _random_view(rng, SHAPE)
-            rhs = _expression(rng, arrays, ext, rng.randrange(1, 4), SHAPE)
+            rhs = _expression(rng, arrays, ext, rng.randrange(1, 4), SHAPE, device_scalars)
             value = np.array(rhs.e, copy=True)   # the right-hand side is evaluated before the write
             target.e[dst] = value
             target.l[dst] = rhs.l
         elif action < 0.75:                   # a new whole array from an expression
-            rhs = _expression(rng, arrays, SHAPE, rng.randrange(1, 4), SHAPE)
+            rhs = _expression(rng, arrays, SHAPE, rng.randrange(1, 4), SHAPE, device_scalars)
             lazy = rhs.l.copy() if isinstance(rhs.l, cnp.ArrayView) else rhs.l   # a bare view aliases its base
             arrays.append(_Pair(np.array(rhs.e, copy=True), lazy))
         elif action < 0.9:                    # literal fill of a region
