@@ -96,6 +96,9 @@ def _program(seed, interface, SHAPE=None):
     rng = random.Random(seed)
     nprng = np.random.default_rng(seed)
     arrays, scalars = [], []
+    # some programs flush by themselves every few ops: results then live across batches
+    if seed % 3 == 1:
+        cnp.set_auto_flush(interface, rng.choice([2, 5, 11]))
     dtype = np.float32 if seed % 5 == 3 else np.float64     # every fifth program in single precision
     for _ in range(3):
         host = nprng.uniform(-2.0, 2.0, SHAPE).astype(dtype)
@@ -105,6 +108,7 @@ def _program(seed, interface, SHAPE=None):
     exact_host = nprng.choice(np.array([-1.0, 0.5, 2.0, 0.25], dtype=dtype), SHAPE)
     exact = _Pair(exact_host.copy(), cnp.asarray(exact_host))
     device_scalars = []
+    products = []       # results of non-fusible nodes (matvec), compared to 1e-10 at the end
     for _ in range(rng.randrange(4, 9)):
         if rng.random() < 0.25:
             if rng.random() < 0.5:
@@ -117,6 +121,14 @@ def _program(seed, interface, SHAPE=None):
         if len(arrays) > 3 and rng.random() < 0.2:
             # drop an array: results nobody holds any more become temporaries of their group
             del arrays[rng.randrange(len(arrays))]
+        if len(SHAPE) == 2 and rng.random() < 0.15:
+            # non-fusible nodes between the groups: a matvec with one of the arrays, and a tile
+            # of a fresh vector that joins the arrays
+            vec_host = nprng.uniform(-1.0, 1.0, (SHAPE[1],)).astype(dtype)
+            vec = _Pair(vec_host, cnp.asarray(vec_host))
+            a = rng.choice(arrays)
+            products.append(_Pair(a.e.astype(np.float64) @ vec.e.astype(np.float64), a.l @ vec.l))
+            arrays.append(_Pair(np.tile(vec.e, (SHAPE[0], 1)), cnp.tile(vec.l, (SHAPE[0], 1))))
         action = rng.random()
         if action < 0.55:                     # region update, possibly reading what it overwrites
             target = rng.choice(arrays)
@@ -142,6 +154,10 @@ def _program(seed, interface, SHAPE=None):
         got = a.l.get(interface)
         assert got.shape == a.e.shape
         assert got.tobytes() == np.ascontiguousarray(a.e).tobytes(), f"seed {seed}: array differs"
+    for pr in products:
+        got = np.asarray(pr.l.get(interface), np.float64)
+        tol = 1e-10 if dtype == np.float64 else 1e-4
+        assert np.max(np.abs(got - pr.e)) <= tol * max(1.0, float(np.max(np.abs(pr.e)))), f"seed {seed}: matvec differs"
     for s in scalars:
         got = float(s.l.get(interface)[0])
         tol = 1e-10 if dtype == np.float64 else 1e-4   # float32 sums: different summation orders
