@@ -53,7 +53,7 @@ class _Pair:
 def _operand(rng, arrays, ext, SHAPE, device_scalars=()):
     kind = rng.random()
     if kind < 0.2:
-        v = rng.choice([0.5, 2.0, -1.25, 3.0])
+        v = rng.choice([2, -1, 3] if arrays[0].e.dtype.kind == "i" else [0.5, 2.0, -1.25, 3.0])
         return _Pair(v, v)
     if kind < 0.3 and device_scalars:
         # a size-1 device array (the alpha and beta of a CG iteration): broadcast like a scalar
@@ -66,13 +66,14 @@ def _operand(rng, arrays, ext, SHAPE, device_scalars=()):
 def _expression(rng, arrays, ext, depth, SHAPE, device_scalars=()):
     if depth == 0 or rng.random() < 0.25:
         x = _operand(rng, arrays, ext, SHAPE, device_scalars)
-        if not isinstance(x.e, np.ndarray):  # keep at least one array in every expression
+        if not isinstance(x.e, np.ndarray) or x.e.ndim == 0:  # keep at least one array in every expression
             y = _operand(rng, arrays, ext, SHAPE)
-            while not isinstance(y.e, np.ndarray):
+            while not isinstance(y.e, np.ndarray) or y.e.ndim == 0:
                 y = _operand(rng, arrays, ext, SHAPE)
             return _Pair(x.e + y.e, x.l + y.l)
         return x
-    op = rng.choice(["+", "-", "*", "/", "abs", "sqrt", "neg"])
+    integer = isinstance(arrays[0].e, np.ndarray) and arrays[0].e.dtype.kind == "i"
+    op = rng.choice(["+", "-", "*", "abs", "neg"] if integer else ["+", "-", "*", "/", "abs", "sqrt", "neg"])
     a = _expression(rng, arrays, ext, depth - 1, SHAPE, device_scalars)
     if op == "abs":
         return _Pair(np.abs(a.e), cnp.abs(a.l))
@@ -99,13 +100,15 @@ def _program(seed, interface, SHAPE=None):
     # some programs flush by themselves every few ops: results then live across batches
     if seed % 3 == 1:
         cnp.set_auto_flush(interface, rng.choice([2, 5, 11]))
-    dtype = np.float32 if seed % 5 == 3 else np.float64     # every fifth program in single precision
+    # every fifth program in single precision, every seventh on integers (no division, no sqrt)
+    dtype = np.float32 if seed % 5 == 3 else (rng.choice([np.int32, np.int64]) if seed % 7 == 2 else np.float64)
+    integer = np.dtype(dtype).kind == "i"
     for _ in range(3):
-        host = nprng.uniform(-2.0, 2.0, SHAPE).astype(dtype)
+        host = (nprng.integers(-3, 4, SHAPE) if integer else nprng.uniform(-2.0, 2.0, SHAPE)).astype(dtype)
         arrays.append(_Pair(host.copy(), cnp.asarray(host)))
     # an array of exactly representable values: its sums and dot products are exact in any order,
     # so that scalars derived from them can flow back into array expressions bit for bit
-    exact_host = nprng.choice(np.array([-1.0, 0.5, 2.0, 0.25], dtype=dtype), SHAPE)
+    exact_host = nprng.choice(np.array([-1, 1, 2, 0] if integer else [-1.0, 0.5, 2.0, 0.25], dtype=dtype), SHAPE)
     exact = _Pair(exact_host.copy(), cnp.asarray(exact_host))
     device_scalars = []
     products = []       # results of non-fusible nodes (matvec), compared to 1e-10 at the end
@@ -115,13 +118,13 @@ def _program(seed, interface, SHAPE=None):
                 device_scalars.append(_Pair(dtype(np.sum(exact.e)), cnp.sum(exact.l)))
             else:
                 device_scalars.append(_Pair(dtype(np.sum(exact.e * exact.e)), cnp.dot2d(exact.l, exact.l)))
-            if len(device_scalars) >= 2 and rng.random() < 0.5:   # scalar-scalar arithmetic on the device
+            if len(device_scalars) >= 2 and rng.random() < 0.5 and not integer:   # scalar-scalar arithmetic on the device
                 a, b = device_scalars[-2], device_scalars[-1]
                 device_scalars.append(_Pair(dtype(a.e / (abs(b.e) + dtype(1.0))), a.l / (cnp.abs(b.l) + 1.0)))
         if len(arrays) > 3 and rng.random() < 0.2:
             # drop an array: results nobody holds any more become temporaries of their group
             del arrays[rng.randrange(len(arrays))]
-        if len(SHAPE) == 2 and rng.random() < 0.15:
+        if len(SHAPE) == 2 and rng.random() < 0.15 and not integer:
             # non-fusible nodes between the groups: a matvec with one of the arrays, and a tile
             # of a fresh vector that joins the arrays
             vec_host = nprng.uniform(-1.0, 1.0, (SHAPE[1],)).astype(dtype)
@@ -144,12 +147,12 @@ def _program(seed, interface, SHAPE=None):
         elif action < 0.9:                    # literal fill of a region
             target = rng.choice(arrays)
             dst, _ = _random_view(rng, SHAPE)
-            v = rng.choice([0.0, 1.0, -3.5])
+            v = rng.choice([0, 1, -3] if integer else [0.0, 1.0, -3.5])
             target.e[dst] = v
             target.l[dst] = v
         else:                                 # reduction of a fresh expression
             rhs = _expression(rng, arrays, SHAPE, 2, SHAPE)
-            scalars.append(_Pair(float(np.sum(rhs.e)), cnp.sum(rhs.l)))
+            scalars.append(_Pair(float(np.sum(rhs.e, dtype=np.int64 if integer else None)), cnp.sum(rhs.l)))
     for a in arrays:
         got = a.l.get(interface)
         assert got.shape == a.e.shape
