@@ -1104,7 +1104,8 @@ int Context::compile_group(const char* blob, int64_t size, uint64_t* handle) {
     int rc = parse_node(blob, size, &node, &err_);
     if (rc) return rc;
     GroupIR g;
-    if ((rc = lower_group(node, {}, &g, &err_, true))) return rc;
+    rc = lower_group(node, {}, &g, &err_, true);
+    if (rc) return rc;
     std::string src;
     if ((rc = generate_source(g, &src, &err_))) return rc;
     if (initialised_) {
