@@ -361,8 +361,12 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
             for (size_t i = 0; i < in_names.size(); ++i)
                 if (in_names[i] == l.name) reach[i] = std::max(reach[i], r);
         }
-        for (size_t i = 0; i < ins.size(); ++i)
+        for (size_t i = 0; i < ins.size(); ++i) {
+            if (reach[i] > ins[i]->halo)
+                return fail(CN_ERR_UNSUPPORTED, "array " + std::to_string(in_names[i]) + " was created with a halo of " +
+                                                    std::to_string(ins[i]->halo) + " rows, the stencil reaches " + std::to_string(reach[i]));
             if (reach[i] > 0 && ins[i]->halo_fresh < reach[i]) stale.push_back(ins[i]);
+        }
         // With a halo deeper than the stencil's reach a sweep can also update rows of the halo
         // itself (the neighbour computes the same values for its own rows), so that the next
         // sweeps need no exchange: one exchange of `halo` rows serves up to halo / reach sweeps.
