@@ -593,8 +593,6 @@ struct Gen {
         o << "  const int lx = threadIdx.x % CN_TX, ly = threadIdx.x / CN_TX;\n";
         o << "  bool timed_out = false;\n";
         if (N == 3 && g.two_domains) o << "  const long long rz0 = a.rlo[0], rz1 = a.rhi[0];\n";
-        const char* ilo = g.two_domains ? "rxlo" : "xlo";
-        const char* ihi = g.two_domains ? "rxhi" : "xhi";
         const std::string dom = g.two_domains ? "a.rlo" : "a.lo";
         const std::string domh = g.two_domains ? "a.rhi" : "a.hi";
 
