@@ -67,7 +67,8 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     if (rc) return fail(rc, "group kernel failed to compile:\n" + k.log);
     stats_.compiles++;
     if ((rc = driver_fail(drv_.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData"))) return rc;
-    if ((rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, g.entry_name().c_str()), "cuModuleGetFunction"))) return rc;
+    rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, g.entry_name().c_str()), "cuModuleGetFunction");
+    if (rc) return rc;
     {
         const char* cls = g.cls == GroupIR::SHIFTED ? (g.flat ? "flat" : "shifted")
                           : (g.cls == GroupIR::STRIDED ? "strided" : "scalar");
