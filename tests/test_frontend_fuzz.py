@@ -60,6 +60,13 @@ def _operand(rng, arrays, ext, SHAPE, device_scalars=()):
         return rng.choice(device_scalars)
     a = rng.choice(arrays)
     sl = _same_extent_view(rng, SHAPE, ext)
+    if rng.random() < 0.15:
+        # the same elements through a view of a view (the outer view trims nothing or one
+        # leading row, the inner slices are shifted accordingly)
+        trim = 1 if sl[0].start >= 1 else 0
+        outer = (slice(trim, None),) + (slice(None),) * (len(SHAPE) - 1)
+        inner = (slice(sl[0].start - trim, sl[0].stop - trim, sl[0].step),) + tuple(sl[1:])
+        return _Pair(a.e[outer][inner], a.l[outer][inner])
     return _Pair(a.e[sl], a.l[sl])
 
 
@@ -140,6 +147,12 @@ def _program(seed, interface, SHAPE=None):
             value = np.array(rhs.e, copy=True)   # the right-hand side is evaluated before the write
             target.e[dst] = value
             target.l[dst] = rhs.l
+        elif action < 0.6 and len(SHAPE) >= 2:   # one row (plane) assigned from another through integer indices
+            target, source = rng.choice(arrays), rng.choice(arrays)
+            i, j = rng.randrange(SHAPE[0]), rng.randrange(SHAPE[0])
+            value = np.array(source.e[j] * 2, copy=True)
+            target.e[i] = value
+            target.l[i] = source.l[j] * 2
         elif action < 0.75:                   # a new whole array from an expression
             rhs = _expression(rng, arrays, SHAPE, rng.randrange(1, 4), SHAPE, device_scalars)
             lazy = rhs.l.copy() if isinstance(rhs.l, cnp.ArrayView) else rhs.l   # a bare view aliases its base
