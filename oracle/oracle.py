@@ -134,6 +134,15 @@ def _slices(region, shape):
     return tuple(slice(a, b, s) for a, b, s in zip(region.start, region.stop, region.step))
 
 
+def _store_scalar(s, dtype):
+    """A reduction result as a size-1 array of the group's element type.  Integer sums are
+    accumulated in 64 bits and then converted like a C cast (two's-complement wrap), which is what
+    the kernels' `(T)total` does."""
+    if np.dtype(dtype).kind == "i":
+        return np.array([int(s)], dtype=np.int64).astype(dtype)
+    return np.array([s], dtype=dtype)
+
+
 class Oracle:
     """Interpreter of DAG nodes over numpy arrays (name -> ndarray)."""
 
@@ -237,14 +246,14 @@ class Oracle:
                         np.dot(np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel())
                 else:
                     s = np.sum(np.asarray(a, np.int64) * np.asarray(b, np.int64))
-                self.arrays[r.result_name] = np.array([s], dtype=dtype)
+                self.arrays[r.result_name] = _store_scalar(s, dtype)
             elif op == OP_SUM:
                 a = self._operand(r.operands[0], values, dtype)
                 if dtype.kind == "f":
                     s = dot(a, np.ones(np.size(a)), ref_tile(np.size(a), 1))
                 else:
                     s = np.sum(np.asarray(a, np.int64))
-                self.arrays[r.result_name] = np.array([s], dtype=dtype)
+                self.arrays[r.result_name] = _store_scalar(s, dtype)
             elif op == OP_MATMUL:
                 A = self.arrays[r.operands[0][0].result_name]
                 A = A[_slices(r.operands[0][1], A.shape)]

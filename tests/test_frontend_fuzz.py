@@ -165,7 +165,8 @@ def _program(seed, interface, SHAPE=None):
             target.l[dst] = v
         else:                                 # reduction of a fresh expression
             rhs = _expression(rng, arrays, SHAPE, 2, SHAPE)
-            scalars.append(_Pair(float(np.sum(rhs.e, dtype=np.int64 if integer else None)), cnp.sum(rhs.l)))
+            total = np.sum(rhs.e, dtype=np.int64).astype(dtype) if integer else np.sum(rhs.e)   # integer sums wrap
+            scalars.append(_Pair(float(total), cnp.sum(rhs.l)))
     for a in arrays:
         got = a.l.get(interface)
         assert got.shape == a.e.shape
