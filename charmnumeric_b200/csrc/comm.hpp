@@ -33,4 +33,29 @@ int comm_allreduce_sum(Comm* c, void* buf, int64_t count, int dtype, cudaStream_
 int comm_broadcast(Comm* c, const void* send, void* recv, int64_t count, int dtype, int root,
                    cudaStream_t s, std::string* err);
 
+// Scope of one NCCL group call.  The group is always closed: by end() on the normal path, by
+// the destructor when an error return leaves the scope early (an open group would swallow
+// every later call of this rank).
+class CommGroup {
+public:
+    explicit CommGroup(std::string* err) : err_(err), rc_(comm_group_start(err)), open_(rc_ == 0) {}
+    ~CommGroup() {
+        std::string ignored;
+        if (open_) comm_group_end(&ignored);
+    }
+    CommGroup(const CommGroup&) = delete;
+    CommGroup& operator=(const CommGroup&) = delete;
+    int started() const { return rc_; }  // status of the group start
+    int end() {
+        if (!open_) return rc_;
+        open_ = false;
+        return comm_group_end(err_);
+    }
+
+private:
+    std::string* err_;
+    int rc_;
+    bool open_;
+};
+
 }  // namespace cn

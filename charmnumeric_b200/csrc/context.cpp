@@ -319,10 +319,11 @@ int Context::setup_peer_boxes() {
     if (rc) return rc;
     char* stage = (char*)scratch_;
     if ((rc = cuda_fail(cudaMemcpyAsync(stage + hs * rank_, &mine_h, hs, cudaMemcpyHostToDevice, stream_), "peer handle"))) return rc;
-    if ((rc = comm_group_start(&err_))) return rc;
+    CommGroup group(&err_);
+    if ((rc = group.started())) return rc;
     for (int p = 0; p < nranks_; ++p)
         if ((rc = comm_broadcast(&comm_, stage + hs * p, stage + hs * p, (int64_t)(hs / 4), DT_I32, p, stream_, &err_))) return rc;
-    if ((rc = comm_group_end(&err_))) return rc;
+    if ((rc = group.end())) return rc;
     std::vector<cudaIpcMemHandle_t> handles(nranks_);
     if ((rc = cuda_fail(cudaMemcpyAsync(handles.data(), stage, hs * nranks_, cudaMemcpyDeviceToHost, stream_), "peer handles"))) return rc;
     if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "peer handles"))) return rc;
@@ -423,7 +424,8 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
         }
     }
     prof_start("halo exchange (nccl)", (double)cnt * esz * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)), st);
-    if ((rc = comm_group_start(&err_))) return rc;
+    CommGroup group(&err_);
+    if ((rc = group.started())) return rc;
     if (has_prev) {
         if ((rc = comm_send(&comm_, a->buf.data, cnt, a->dtype, rank_ - 1, st, &err_))) return rc;
         if ((rc = comm_recv(&comm_, a->buf.data - cnt * esz, cnt, a->dtype, rank_ - 1, st, &err_))) return rc;
@@ -432,7 +434,7 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
         if ((rc = comm_send(&comm_, a->buf.data + (nl * a->unit - cnt) * esz, cnt, a->dtype, rank_ + 1, st, &err_))) return rc;
         if ((rc = comm_recv(&comm_, a->buf.data + nl * a->unit * esz, cnt, a->dtype, rank_ + 1, st, &err_))) return rc;
     }
-    if ((rc = comm_group_end(&err_))) return rc;
+    if ((rc = group.end())) return rc;
     prof_stop();
     a->halo_fresh = a->halo;
     stats_.halo_exchanges++;

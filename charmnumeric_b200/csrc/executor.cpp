@@ -544,7 +544,8 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         bool done = false;
         if (overlap && !empty) {
             // rows [0, H) and [nl - H, nl) of the slab read halo rows; everything between does not
-            const int64_t H = halo_, nl = re - rb;
+            // (H is the stencil's own reach along dimension 0, whatever depth the option holds now)
+            const int64_t H = std::max<int64_t>(g.max_halo, 1), nl = re - rb;
             const int64_t i0 = std::max<int64_t>(lo[0], H), i1 = std::min<int64_t>(hi[0], nl - H);
             if (i1 - i0 >= 4 * H && (rc = ensure_second_stream()) == CN_OK) {
                 const double row_bytes = bytes / (double)(hi[0] - lo[0]);
@@ -587,8 +588,19 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     }
     for (size_t m = 0; m < outs.size(); ++m) {
         Array* x = outs[m];
-        if (g.copy_through && g.outs[m].hazard) std::swap(x->buf, x->shadow);
-        x->halo_fresh = (int)ext;  // the widened sweep left that many halo rows up to date
+        const bool through = g.copy_through && g.outs[m].hazard;
+        if (through) std::swap(x->buf, x->shadow);
+        // The widened sweep left `ext` halo rows up to date where it wrote them.  An assignment
+        // that is not copied through writes the region only: halo cells outside it (the side
+        // columns of a two-array ping-pong sweep, a physical edge row inside the halo) keep
+        // what they held, so they are only as fresh as the halo was before.
+        int fresh = (int)ext;
+        if (g.outs[m].is_set && !through) {
+            bool whole = g.reg_lo[0] <= 0 && g.reg_hi[0] >= x->shape[0];
+            for (int d = 1; d < nd; ++d) whole = whole && g.reg_lo[d] <= 0 && g.reg_hi[d] >= x->shape[d];
+            if (!whole) fresh = std::min(fresh, x->halo_fresh);
+        }
+        x->halo_fresh = fresh;
     }
     if (ext > 0) stats_.deep_halo_sweeps++;
     for (auto& sw : swaps) {
@@ -844,14 +856,15 @@ int Context::execute_matmul(const AstNode& r) {
         return fail(CN_ERR_UNSUPPORTED, "sliced matvec needs a single rank");
     if (!comm_.ready) return fail(CN_ERR_COMM, "matvec across ranks needs cn_comm_init first");
     if ((rc = ensure_scratch((size_t)cols * esz + 256))) return rc;
-    if ((rc = comm_group_start(&err_))) return rc;
+    CommGroup group(&err_);
+    if ((rc = group.started())) return rc;
     for (int p = 0; p < nranks_; ++p) {
         int64_t b, e;
         partition(cols, &b, &e, p);
         if (e <= b) continue;
         if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * esz, e - b, dtype, p, stream_, &err_))) return rc;
     }
-    if ((rc = comm_group_end(&err_))) return rc;
+    if ((rc = group.end())) return rc;
     prof_start("matvec", ((double)A->local_rows() * cols + A->local_rows() + cols) * esz);
     rc = cuda_fail(launch_matvec(A->buf.data, A->shape[1], scratch_, y->buf.data, A->local_rows(), cols, dtype, stream_), "matvec");
     prof_stop();
@@ -959,14 +972,15 @@ int Context::execute_tile(const AstNode& r) {
     if (nranks_ > 1 && !x->replicated) {
         if (!comm_.ready) return fail(CN_ERR_COMM, "TILE across ranks needs cn_comm_init first");
         if ((rc = ensure_scratch((size_t)x->global_elems() * esz + 256))) return rc;
-        if ((rc = comm_group_start(&err_))) return rc;
+        CommGroup group(&err_);
+    if ((rc = group.started())) return rc;
         for (int p = 0; p < nranks_; ++p) {
             int64_t b, e;
             partition(x->shape[0], &b, &e, p);
             if (e <= b) continue;
             if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * x->unit * esz, (e - b) * x->unit, dtype, p, stream_, &err_))) return rc;
         }
-        if ((rc = comm_group_end(&err_))) return rc;
+        if ((rc = group.end())) return rc;
         src = scratch_;
     }
     rc = cuda_fail(launch_tile(out->buf.data, oshape, out->row_begin, out->local_rows(), src, sshape, dtype, stream_), "tile");
@@ -1042,14 +1056,15 @@ int Context::get(int name, int64_t count, int dtype, void* out) {
     if (!comm_.ready) return fail(CN_ERR_COMM, "get across ranks needs cn_comm_init first");
     if ((rc = ensure_scratch(count * esz + 256))) return rc;
     x = find(name);
-    if ((rc = comm_group_start(&err_))) return rc;
+    CommGroup group(&err_);
+    if ((rc = group.started())) return rc;
     for (int p = 0; p < nranks_; ++p) {
         int64_t b, e;
         partition(x->shape[0], &b, &e, p);
         if (e <= b) continue;
         if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * x->unit * esz, (e - b) * x->unit, dtype, p, stream_, &err_))) return rc;
     }
-    if ((rc = comm_group_end(&err_))) return rc;
+    if ((rc = group.end())) return rc;
     if ((rc = cuda_fail(cudaMemcpyAsync(out, scratch_, count * esz, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
     stats_.bytes_d2h += count * esz;
     return synchronize();

@@ -11,7 +11,7 @@
 // same deterministic two-pass scheme as the regular dot kernel, but its scratch -- one partial
 // per 8192-element block plus the ticket counter -- lives in a fixed array that is part of
 // the library image.  The caller supplies the inputs and the output as device pointers and
-// nothing is allocated or freed, here or in any library routine called from here.
+// this function makes no allocation or free of its own.
 //
 // Limits and rules
 //   * n <= CN_NOALLOC_MAX_ELEMS (2^28 elements, 2 GiB per operand): the scratch holds one
@@ -19,8 +19,11 @@
 //   * Every GPU that loads the library carries the 256 KiB scratch array until the process
 //     exits.
 //   * The first call on a device looks up the device address of the scratch array
-//     (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
-//     outside any stream capture.
+//     (cudaGetSymbolAddress, with that device current) and remembers it.  With CUDA's lazy
+//     module loading that same call makes the driver place the library's device image -- the
+//     scratch array and the exp tables -- in device memory, which is an allocation by the
+//     driver.  So make the first call as a warm-up (n = 0 will do) while memory is still
+//     available and outside any stream capture; only later calls are allocation-free.
 //   * All calls on a device share the scratch.  It keeps whatever the previous call left; the
 //     ticket counter is cleared on the stream before each launch.  Two calls whose kernels
 //     overlap on the GPU (different streams without ordering) race on it: order them.

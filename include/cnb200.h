@@ -143,10 +143,13 @@ int cn_profile_report(cn_context* ctx, char* buf, int64_t cap);
  * the application has claimed all memory as its own arena, on an out-of-memory error path,
  * or where touching the allocator is ruled out for latency or determinism.  The per-block
  * partial sums of the deterministic two-pass reduction live in a fixed 256 KiB array inside
- * the library image instead of an allocated buffer; neither this call nor anything it calls
- * allocates or frees.  Limit: n <= CN_NOALLOC_MAX_ELEMS (one partial per 8192 elements),
- * otherwise CN_STATUS_LIMIT and nothing is launched.  The first call on a device resolves the
- * array's device address: make it outside stream capture.  All calls on a device share the
+ * the library image instead of an allocated buffer; this call makes no allocation or free of
+ * its own.  Limit: n <= CN_NOALLOC_MAX_ELEMS (one partial per 8192 elements), otherwise
+ * CN_STATUS_LIMIT and nothing is launched.  The first call on a device resolves the array's
+ * device address, and with CUDA's lazy module loading it is also the moment the driver puts
+ * the library's device image (this array included) into device memory: make that first call
+ * as a warm-up (n = 0 is enough) while memory is still available and outside stream capture;
+ * only the calls after it are allocation-free.  All calls on a device share the
  * array (the ticket counter is cleared on the stream before each launch); calls whose
  * kernels may overlap on the GPU race on it and must be ordered by the caller.  Needs no
  * context. */

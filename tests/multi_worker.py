@@ -64,6 +64,22 @@ def main():
         h0 = cnp.random.uniform((37,), seed=41)
         m = cnp.random.uniform((5, 6), seed=42)
         return {"rows": cnp.tile(h0, (11, 1)), "blocks": cnp.tile(m, (3, 2)), "cube": cnp.tile(h0, (2, 3, 1))}
+    def pingpong():
+        # two arrays written in turn, side boundaries that are not zero: a sweep writes the
+        # interior region only, so the halo cells of the side columns keep what they held
+        n0, n1 = 67, 130
+        x = cnp.random.uniform((n0, n1), seed=51)
+        xn = cnp.zeros((n0, n1))
+        for u in (x, xn):
+            u[0, :] = 1.0
+            u[-1, :] = 0.5
+            u[:, 0] = 1.0
+            u[:, -1] = 2.0
+        for it in range(11):
+            xn[1:-1, 1:-1] = 0.25 * (x[:-2, 1:-1] + x[2:, 1:-1] + x[1:-1, :-2] + x[1:-1, 2:])
+            x, xn = xn, x
+        return {"x": x, "xn": xn}
+    progs["jacobi2d_pingpong"] = pingpong
     progs["chain"] = chain
     progs["diag"] = diag
     progs["tile"] = tile

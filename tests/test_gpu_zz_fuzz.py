@@ -1,11 +1,8 @@
 """The seeded random programs of tests/test_frontend_fuzz.py on the CUDA path: every array the
 GPU produces must be bit-identical to NumPy's eager evaluation of the same program (only
 IEEE-exact operations are generated: +, -, *, /, abs, sqrt; division and square root are
-compiled IEEE-rounded), reductions and matvec within 1e-10.
-
-Marked xfail(strict=False) because these programs have not yet been run on a GPU: a pass
-shows up as XPASS, a mismatch as XFAIL with the seed in the message, and neither stops the
-rest of the suite."""
+compiled IEEE-rounded), reductions and matvec within 1e-10.  A mismatch fails the suite, with
+the seed in the message."""
 import pytest
 
 import charmnumeric_b200 as cnp
@@ -14,7 +11,6 @@ from tests import test_frontend_fuzz as T
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.xfail(reason="random programs not yet run on a GPU", strict=False)
 @pytest.mark.parametrize("seed", [3, 4, 5, 6, 8, 13, 16, 21, 1001, 1003, 1004, 1006])
 def test_random_program_on_the_gpu(interface, seed):
     cnp.reset_frontend_state()

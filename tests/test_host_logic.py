@@ -241,3 +241,33 @@ def test_shape_mismatch_is_reported_by_the_frontend():
         cnp.zeros((4,)) + cnp.zeros((5,))
     with pytest.raises(ValueError):
         cnp.zeros((4, 3)) @ cnp.zeros((4,))
+
+
+def test_exp_tables_of_oracle_and_device_are_identical():
+    """The oracle's C table and the device table come from two generator scripts; exp and tanh
+    are only bit-identical between the two while every entry and the ln2 split agree."""
+    import re
+    root = Path(__file__).resolve().parent.parent
+    dev = (root / "charmnumeric_b200" / "csrc" / "cn_exp_table.inc").read_text()
+    orc = (root / "oracle" / "cn_oracle_exp_table.h").read_text()
+    hexf = r"-?0x[0-9a-f.]+p[-+]?\d+"
+
+    def block(text, start, end):
+        i = text.index(start)
+        j = text.index(end, i)
+        return [float.fromhex(v) for v in re.findall(hexf, text[i + len(start):j])]
+    dev_hi = block(dev, "#define CN_EXP_TABLE_HI", "#define CN_EXP_TABLE_LO")
+    dev_lo = block(dev, "#define CN_EXP_TABLE_LO", "#define CN_EXP_TABLE_PAIRS")
+    dev_pairs = block(dev, "#define CN_EXP_TABLE_PAIRS", "#define CN_LN2_64_HI")
+    orc_hi = block(orc, "CNO_T_HI[64] = {", "};")
+    orc_lo = block(orc, "CNO_T_LO[64] = {", "};")
+    assert len(dev_hi) == len(dev_lo) == 64 and len(dev_pairs) == 128
+    assert [v.hex() for v in dev_hi] == [v.hex() for v in orc_hi]
+    assert [v.hex() for v in dev_lo] == [v.hex() for v in orc_lo]
+    assert [v.hex() for v in dev_pairs[0::2]] == [v.hex() for v in orc_hi]
+    assert [v.hex() for v in dev_pairs[1::2]] == [v.hex() for v in orc_lo]
+    consts_dev = [float.fromhex(re.search(name + r"\s+(" + hexf + ")", dev).group(1))
+                  for name in ("CN_LN2_64_HI", "CN_LN2_64_LO", "CN_INV_LN2_64")]
+    consts_orc = [float.fromhex(re.search(name + r"\s*=\s*(" + hexf + ")", orc).group(1))
+                  for name in ("CNO_C_HI", "CNO_C_LO", "CNO_INV")]
+    assert [v.hex() for v in consts_dev] == [v.hex() for v in consts_orc]

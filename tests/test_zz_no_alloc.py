@@ -3,9 +3,11 @@ memory (its scratch is a fixed array inside the library instead of an allocated 
 
 The test hands the entry point raw device pointers (torch owns the memory here, as such a
 caller's own arena would), calls it twice in a row -- the second call finds the scratch as
-the first one left it -- and compares each result with what the regular path (a REDUCE node
-through cn_receive_dag, read back with cn_get) gives for the same data, within the
-tolerance the reduction tests use.  Collected last on purpose (file name), so a failure
+the first one left it -- and compares each result with the CPU oracle's dot product of the
+same host arrays and, as a second check, with what the regular path (a REDUCE node through
+cn_receive_dag, read back with cn_get) gives for the same data, both within the tolerance the
+reduction tests use.  A first call with n = 0 plays the warm-up a caller makes while memory
+is still available (it loads the library's device image and resolves the scratch address).  Collected last on purpose (file name), so a failure
 here cannot hide the result of any other test; it needs nothing from the tests before it.
 """
 import ctypes as C
@@ -33,13 +35,20 @@ def test_dot_noalloc_matches_regular_dot_twice(n):
     from charmnumeric_b200 import Context, _lib
     lib = _lib.load()
     torch.cuda.set_device(0)
+    from oracle import oracle as O
     ctx = Context(device=0)
     try:
+        warm = torch.full((1,), float("nan"), dtype=torch.float64, device="cuda")
+        assert lib.cn_dot_noalloc(C.c_void_p(warm.data_ptr()), C.c_void_p(warm.data_ptr()), 0,
+                                  C.c_void_p(warm.data_ptr()), None) == 0
+        torch.cuda.synchronize()
+        assert float(warm.cpu()[0]) == 0.0
         for call in range(2):
             rng = np.random.default_rng(100 + call)
             a = rng.uniform(-1.0, 1.0, n)
             b = rng.uniform(-1.0, 1.0, n)
-            want = _regular_dot(ctx, 9100, 9101, 9102, a, b)
+            want = float(O.dot(a, b))
+            regular = _regular_dot(ctx, 9100, 9101, 9102, a, b)
             ta = torch.from_numpy(a).cuda()
             tb = torch.from_numpy(b).cuda()
             out = torch.full((1,), float("nan"), dtype=torch.float64, device="cuda")
@@ -50,6 +59,7 @@ def test_dot_noalloc_matches_regular_dot_twice(n):
             torch.cuda.synchronize()
             got = float(out.cpu()[0])
             assert abs(got - want) <= RTOL * max(abs(want), 1e-300) + 1e-300, (n, call, got, want)
+            assert abs(got - regular) <= RTOL * max(abs(want), 1e-300) + 1e-300, (n, call, got, regular)
     finally:
         ctx.close()
 
