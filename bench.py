@@ -7,20 +7,34 @@
 One step = one pass of the hot path: one CG iteration (default workload, configuration C3:
 matrix-free CG on the 2-D Poisson 5-point operator, 8192 x 8192 unknowns per GPU), one Jacobi
 sweep, one fused-chain repeat or one power-iteration step.  Inputs are synthetic, generated on
-the device from a seed; the working set (five 537 MB arrays for CG) is far larger than L2.
+the device from a seed; every working set but Jacobi2D's (64 MiB, which the configuration
+fixes) is far larger than L2.
 
-Timed quantities
+The JSON line carries the named workload at the top level and, under "workloads", the same
+figures for the other four configurations at the same number of GPUs.
+
+Before anything is timed, an untimed check leg runs small seeded problems (Jacobi 2-D / 3-D at
+two halo depths, CG, the chain, a matvec) through the C ABI on all N ranks and through the CPU
+oracle on the same DAG, and compares them ("check" in the JSON line); the process exits
+non-zero when a case fails.
+
+Timed quantities, per workload
   value     K steps enqueued back to back, CUDA events on the library's own stream, barrier and
-            device synchronisation on both sides, maximum over ranks.
+            device synchronisation on both sides, maximum over ranks; that burst is repeated at
+            least five times (and for at least a second, so that the clock sampler sees it) and
+            the median burst is reported, with the fastest and slowest beside it.
   e2e       the same K steps, each one submitted from the host as a DAG blob through
             cn_receive_dag and followed by a device->host read of the step's scalar result
             through cn_get (host buffers on both sides, one synchronisation per step).
+  e2e_solve (CG) a whole solve through the C ABI: the right-hand side goes up from pinned host
+            memory (cn_put_local), K iterations run, the solution comes back (cn_get_local).
   roofline  the dominant kernel's algorithmic bytes / its mean launch duration, taken from the
             library's per-kernel CUDA-event records over a further K profiled steps.
-  cpu_baseline  the oracle's C loops (reference-structured, OpenMP) on this box's host cores,
-            a bounded number of steps of the same workload (rank 0, N = 1 only).
+  cpu_baseline  the oracle's C loops (OpenMP) on this box's host cores, a bounded number of
+            steps of the same workload (rank 0, N = 1 only).
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -34,6 +48,8 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 PEAKS_FALLBACK_GBS = 6650.0
+ALL_WORKLOADS = ["cg", "jacobi2d", "jacobi3d", "chain", "matvec"]
+DEFAULT_HALO = {"jacobi2d": 8}  # rows per side at N > 1; every other workload uses 1
 
 
 def measured_peak():
@@ -44,9 +60,9 @@ def measured_peak():
         return PEAKS_FALLBACK_GBS, "fallback"
 
 
-def dram_traffic(kernel, wl):
-    """DRAM bytes per launch of the dominant kernel, from the committed ncu capture of that
-    kernel (profiles/dram_traffic.json: measured dram read+write bytes per algorithmic byte on a
+def dram_traffic(kernel):
+    """DRAM bytes per launch of a kernel, from the committed ncu capture of that kernel
+    (profiles/dram_traffic.json: measured dram read+write bytes per algorithmic byte on a
     reduced-size case; traffic of these streaming kernels grows in proportion to the points
     processed).  None when no capture covers the kernel."""
     try:
@@ -62,8 +78,9 @@ def dram_traffic(kernel, wl):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 100 ms while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clocks / throttle reasons sampled every 100 ms; stop() keeps the samples
+    whose time stamp falls inside the window it is given."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -80,7 +97,7 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, window=None):
         if self.proc is None:
             return None
         try:
@@ -88,25 +105,36 @@ class ClockSampler:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             return None
-        sm, smax, reasons = [], [], set()
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
+                sm, smax = float(f[1]), float(f[2])
             except ValueError:
                 continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+            try:
+                stamp = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+            except ValueError:
+                stamp = None
+            try:
+                power = float(f[3])
+            except ValueError:
+                power = 0.0
+            active = [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]
+            rows.append((stamp, sm, smax, power, active))
+        if not rows:
             return None
-        busy = [v for v in sm if v > 0.5 * max(sm)] or sm
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(smax),
-                "reasons": sorted(reasons), "samples": len(sm)}
+        inside = rows
+        if window is not None:
+            inside = [r for r in rows if r[0] is not None and window[0] <= r[0] <= window[1]] or rows
+        sm = [r[1] for r in inside]
+        reasons = sorted({n for r in inside for n in r[4]})
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(r[2] for r in inside),
+                "power_w_max": max(r[3] for r in inside), "reasons": reasons,
+                "samples": len(inside), "samples_outside_window": len(rows) - len(inside)}
 
 
 def dist_setup(world):
@@ -132,6 +160,15 @@ def max_over_ranks(dist, value):
     return float(t[0])
 
 
+def min_over_ranks(dist, value):
+    if dist is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return float(t[0])
+
+
 def sum_over_ranks(dist, value):
     if dist is None:
         return value
@@ -139,6 +176,19 @@ def sum_over_ranks(dist, value):
     t = torch.tensor([float(value)], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t[0])
+
+
+def gather_bytes_fn(dist, world):
+    """Every rank's byte string, on every rank (the check leg compares reduction results
+    across ranks with it)."""
+    if dist is None:
+        return None
+
+    def gather(b):
+        out = [None] * world
+        dist.all_gather_object(out, bytes(b))
+        return out
+    return gather
 
 
 def share_unique_id(dist, rank):
@@ -151,11 +201,38 @@ def share_unique_id(dist, rank):
     return bytes(buf.tolist())
 
 
+def pinned_array(shape):
+    """float64 host array in page-locked memory (plain numpy when pinning is not possible)."""
+    import numpy as np
+    try:
+        import torch
+        n = 1
+        for s in shape:
+            n *= int(s)
+        return torch.empty(n, dtype=torch.float64, pin_memory=True).numpy().reshape(shape), True
+    except Exception:
+        return np.empty(shape, dtype=np.float64), False
+
+
+def config_for(name, world, scale, halo):
+    """The configuration block of a JSON line; the GPU arm and the CPU arm print the same one."""
+    from charmnumeric_b200.workloads import WORKLOADS
+    w = WORKLOADS[name]
+    weak = w.scaling == "weak"
+    return {"workload": w.describe(world, scale)["description"],
+            "l2": ("64 MiB working set, fixed by the configuration: served from L2 once warm; no flush"
+                   if name == "jacobi2d" and scale <= 1.0
+                   else "working set far larger than L2; no flush"),
+            "parallelism": f"slab{world}", "scale": scale, "halo_depth": halo if world > 1 else 0,
+            "aggregate": ("value = GPUs x iterations/s of the per-GPU slab" if weak and world > 1
+                          else "value = steps/s of the whole problem")}
+
+
 # ---- CPU baseline (oracle; never on the product path) -------------------------------------------
 
 def cpu_baseline(workload, scale, steps, threads):
-    """Time the oracle's reference-structured C loops on the host: `steps` steps of the same
-    workload.  Returns (steps_per_second, description)."""
+    """Time the oracle's OpenMP C loops on the host: `steps` steps of the same workload.
+    Returns (steps_per_second, description)."""
     import numpy as np
     from oracle import oracle as O
     lib = O.clib()
@@ -220,24 +297,28 @@ def cpu_baseline(workload, scale, steps, threads):
     raise ValueError(workload)
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, world):
+    """The CPU arm: the oracle's loops for the named workload on all host cores, rank 0 only.
+    It runs the per-GPU problem of the N = 1 run once; its configuration block and its step
+    and warm-up counts are the GPU arm's."""
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    steps = max(1, args.steps)
-    for _ in range(min(args.warmup, 1)):
-        cpu_baseline(args.workload, args.scale, 1, threads)
-    value, sample = cpu_baseline(args.workload, args.scale, steps, threads)
     from charmnumeric_b200.workloads import WORKLOADS
+    threads = os.cpu_count() or 1
+    K, W = max(1, args.steps), max(3, args.warmup)
+    halo = args.halo if args.halo > 0 else DEFAULT_HALO.get(args.workload, 1)
+    cpu_baseline(args.workload, args.scale, W, threads)  # warm-up steps, untimed
+    value, sample = cpu_baseline(args.workload, args.scale, K, threads)
     w = WORKLOADS[args.workload]
     line = {
         "impl": "reference", "metric": w.metric, "value": value, "unit": w.unit,
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+        "n_gpus": args.gpus, "steps": K, "warmup": W,
         "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": w.scaling,
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": args.workload, "note": "CPU restatement of the reference path "
-                   "(the reference's own Charm++/MLIR binary cannot be built on this box); one "
-                   "rank-0 process, per-GPU problem size of the N=1 run"},
+        "config": config_for(args.workload, world, args.scale, halo),
+        "note": ("CPU restatement of the reference path (the reference's own Charm++/MLIR binary "
+                 "cannot be built on this box); one rank-0 process runs the per-GPU problem size "
+                 "of the N = 1 run on all host cores"),
         "cpu_baseline": {"value": value, "unit": w.unit, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -248,22 +329,75 @@ def run_reference(args, rank):
 
 # ---- GPU arm ----------------------------------------------------------------------------------------
 
-def run_gpu(args, rank, world, local_rank):
+def timed_bursts(ctx, dist, wl, K, step_index, min_bursts, min_total_ms, max_bursts=400):
+    """Bursts of K steps, each bracketed by a barrier and a device synchronisation and timed
+    with CUDA events on the library's stream (maximum over ranks).  Every rank sees the same
+    maxima, so all ranks run the same number of bursts."""
+    times = []
+    total = 0.0
+    while len(times) < min_bursts or (total < min_total_ms and len(times) < max_bursts):
+        barrier(dist)
+        ctx.synchronize()
+        ctx.timer_start()
+        for _ in range(K):
+            wl.run_step(step_index)
+            step_index += 1
+        ms = max_over_ranks(dist, ctx.timer_stop())
+        times.append(ms)
+        total += ms
+    barrier(dist)
+    return times, step_index
+
+
+def e2e_solve(ctx, dist, wl, K, rank):
+    """A whole CG solve through the C ABI with host buffers on both ends: this rank's slab of
+    the right-hand side goes up from pinned host memory, K iterations run, this rank's slab of
+    the solution comes back into pinned host memory."""
+    import numpy as np
+    info = ctx.array_info(wl.b.name)
+    rb, re = info["rows"]
+    m0, m1 = wl.shape
+    host_b, pinned = pinned_array((re - rb, m1))
+    host_x, _ = pinned_array((re - rb, m1))
+    rng = np.random.default_rng(0x5EED + 33 + rank)
+    host_b[...] = rng.random((re - rb, m1))
+    host_b[:, 0] = 0.0
+    host_b[:, -1] = 0.0
+    if rb == 0:
+        host_b[0, :] = 0.0
+    if re == m0:
+        host_b[-1, :] = 0.0
+    seconds = []
+    for _ in range(3):
+        barrier(dist)
+        ctx.synchronize()
+        t0 = time.perf_counter()
+        ctx.put_local(wl.b.name, wl.shape, host_b)
+        ctx.receive_dag(wl.init_blob)
+        for i in range(K):
+            wl.run_step(i)
+        ctx.get_local_into(wl.x.name, host_x)  # waits for the stream
+        seconds.append(max_over_ranks(dist, time.perf_counter() - t0))
+    finite = bool(np.isfinite(host_x).all())
+    return {"seconds": statistics.median(seconds), "h2d_bytes": int(host_b.nbytes), "d2h_bytes": int(host_x.nbytes),
+            "pinned": pinned, "solution_finite": finite}
+
+
+def measure(name, args, itf, dist, rank, world, local_rank, primary):
+    """Everything that is measured for one workload; returns the dict that goes into the JSON
+    line (rank 0) or None (other ranks)."""
     import charmnumeric_b200 as cnp
     from charmnumeric_b200.workloads import WORKLOADS
 
-    dist = dist_setup(world)
-    uid = share_unique_id(dist, rank) if world > 1 else None
-    itf = cnp.CharmNumericInterface(device=local_rank, rank=rank, nranks=world, unique_id=uid)
     ctx = itf.context
     cnp.reset_frontend_state()
-    # halo depth: sweeps without a fused reduction also update the halo rows they can, so a
-    # deeper halo means fewer exchanges (Jacobi2D: one per 8 sweeps; measured no gain for the
-    # 8 MiB planes of Jacobi3D, whose exchange is bandwidth, not latency)
-    halo = args.halo if args.halo > 0 else {"jacobi2d": 8}.get(args.workload, 1)
+    halo = args.halo if args.halo > 0 else DEFAULT_HALO.get(name, 1)
     if world > 1:
         ctx.set_option("halo", halo)
-    wl = WORKLOADS[args.workload](itf, nranks=world, scale=args.scale)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a few hundred ms before its first sample
+    wl = WORKLOADS[name](itf, nranks=world, scale=args.scale)
     K, W = max(1, args.steps), max(3, args.warmup)
 
     # every distinct step blob once, so that no run-time compilation lands in a timed region
@@ -276,21 +410,15 @@ def run_gpu(args, rank, world, local_rank):
         step_index += 1
     ctx.synchronize()
 
-    # ---- device-timed region ----
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    # ---- device-timed region: repeated bursts of K steps ----
     stats0 = ctx.stats()
-    barrier(dist)
+    t_begin = datetime.datetime.now()
+    times, step_index = timed_bursts(ctx, dist, wl, K, step_index, 5, 1200.0 if primary else 800.0)
     ctx.synchronize()
-    ctx.timer_start()
-    for _ in range(K):
-        wl.run_step(step_index)
-        step_index += 1
-    ms = ctx.timer_stop()
-    barrier(dist)
+    t_end = datetime.datetime.now()
     stats1 = ctx.stats()
-    ms = max_over_ranks(dist, ms)
+    clocks = sampler.stop((t_begin, t_end)) if rank == 0 else None
+    ms = statistics.median(times)
     launches = sum_over_ranks(dist, stats1["kernel_launches"] - stats0["kernel_launches"])
 
     # ---- end to end: host blob in, scalar result out, every step ----
@@ -313,22 +441,12 @@ def run_gpu(args, rank, world, local_rank):
         step_index += 1
     prof = ctx.profile_report()
     ctx.profile(False)
-    # The sampler runs through the device-timed, end-to-end and profiled passes (same workload).
-    # nvidia-smi needs a few hundred ms before its first sample: when the three passes together
-    # were shorter than 1.5 s, the same steps keep running under the sampler until that much
-    # load has been seen.  The count derives from the rank-maximum time, so all ranks agree.
-    extra = 0
-    if 3.0 * ms < 1500.0:
-        extra = min(500000, int((1500.0 - 3.0 * ms) / max(ms / K, 1e-4)) + 1)
-        for _ in range(extra):
-            wl.run_step(step_index)
-            step_index += 1
-        ctx.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["window"] = ("timed + end-to-end + profiled passes" if not extra else
-                            f"timed + end-to-end + profiled passes + {extra} more steps of the same workload")
 
+    solve = None
+    if name == "cg" and primary:
+        solve = e2e_solve(ctx, dist, wl, K, rank)
+
+    entry = None
     if rank == 0:
         peak, peak_kind = measured_peak()
         roofline = None
@@ -342,22 +460,19 @@ def run_gpu(args, rank, world, local_rank):
                                 "share": r["ms"] / total_ms, "gbs": gbs})
             top = kernels[0]
             roofline = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
-                        "frac": top["gbs"] / peak, "traffic": dram_traffic(top, wl), "kernel": top["kernel"],
+                        "frac": top["gbs"] / peak, "traffic": dram_traffic(top), "kernel": top["kernel"],
                         "peak_kind": peak_kind, "nominal_frac": top["gbs"] / 8000.0}
         # weak scaling: every GPU iterates its own slab of the (N times larger) global grid, so the
         # whole-job figure is GPUs x iterations/s; strong scaling: one fixed problem, steps/s
         agg = world if wl.scaling == "weak" else 1
-        value = agg * K / (ms * 1e-3)
         step_gbs = wl.bytes_per_step / world / (ms / K * 1e-3) / 1e9
-        line = {
-            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": wl.scaling,
-            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": wl.description, "l2": "working set far larger than L2; no flush",
-                       "parallelism": f"slab{world}", "scale": args.scale,
-                       "halo_depth": halo if world > 1 else 0,
-                       "aggregate": ("value = GPUs x iterations/s of the per-GPU slab" if agg > 1
-                                     else "value = steps/s of the whole problem")},
+        entry = {
+            "name": name, "metric": wl.metric, "value": agg * K / (ms * 1e-3), "unit": wl.unit,
+            "ms_per_step": ms / K, "scaling": wl.scaling,
+            "bursts": {"count": len(times), "steps_each": K, "median_ms": ms, "min_ms": min(times),
+                       "max_ms": max(times), "value_best": agg * K / (min(times) * 1e-3),
+                       "value_worst": agg * K / (max(times) * 1e-3)},
+            "config": config_for(name, world, args.scale, halo),
             "roofline": roofline,
             "step_hbm": {"algorithmic_bytes_per_step_per_gpu": wl.bytes_per_step / world,
                          "gbs_per_gpu": step_gbs, "frac_of_" + peak_kind: step_gbs / peak,
@@ -368,24 +483,80 @@ def run_gpu(args, rank, world, local_rank):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if solve is not None:
+            entry["e2e_solve"] = {
+                "value": agg * K / solve["seconds"], "unit": wl.unit, "iterations": K,
+                "seconds": solve["seconds"], "h2d_bytes_per_gpu": solve["h2d_bytes"],
+                "d2h_bytes_per_gpu": solve["d2h_bytes"], "pinned_host_memory": solve["pinned"],
+                "solution_finite": solve["solution_finite"],
+                "what": "cn_put_local of the right-hand side + K iterations + cn_get_local of the solution"}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             try:
                 budget_steps = {"cg": 12, "jacobi2d": 200, "jacobi3d": 3, "chain": 3, "matvec": 5}
-                v, sample = cpu_baseline(args.workload, args.scale, budget_steps[args.workload], threads)
-                line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
-                                        "sample": sample}
-                if threads > 4:
+                v, sample = cpu_baseline(name, args.scale, budget_steps[name], threads)
+                entry["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
+                                         "sample": sample}
+                if threads > 4 and primary:
                     # the reference's own test set-up runs on four PEs (charmrun +p4)
-                    v4, _ = cpu_baseline(args.workload, args.scale, max(1, budget_steps[args.workload] // 2), 4)
-                    line["cpu_baseline"]["p4"] = {"value": v4, "cores": 4}
+                    v4, _ = cpu_baseline(name, args.scale, max(1, budget_steps[name] // 2), 4)
+                    entry["cpu_baseline"]["p4"] = {"value": v4, "cores": 4}
             except Exception as exc:  # the baseline is a report, never a gate
-                line["cpu_baseline"] = {"error": repr(exc)}
+                entry["cpu_baseline"] = {"error": repr(exc)}
+    wl.release()
+    ctx.synchronize()
+    barrier(dist)
+    return entry
+
+
+def run_gpu(args, rank, world, local_rank):
+    import charmnumeric_b200 as cnp
+
+    dist = dist_setup(world)
+    uid = share_unique_id(dist, rank) if world > 1 else None
+    itf = cnp.CharmNumericInterface(device=local_rank, rank=rank, nranks=world, unique_id=uid)
+    ctx = itf.context
+    K, W = max(1, args.steps), max(3, args.warmup)
+
+    # ---- untimed check leg: small seeded problems against the CPU oracle, on all N ranks ----
+    check = None
+    if not args.no_check:
+        import __graft_entry__ as entry_points
+        check = entry_points.check_cases(itf, world, gather_bytes_fn(dist, world))
+        everyone_ok = min_over_ranks(dist, 1.0 if check["ok"] else 0.0) > 0.5
+        check["ok_on_all_ranks"] = everyone_ok
+        if not check["ok"]:
+            print(f"[bench] rank {rank}: check failed: "
+                  f"{[c for c in check['cases'] if not c['ok']]}", file=sys.stderr, flush=True)
+
+    names = [args.workload] + ([] if args.only else [w for w in ALL_WORKLOADS if w != args.workload])
+    entries = []
+    for i, name in enumerate(names):
+        entries.append(measure(name, args, itf, dist, rank, world, local_rank, primary=(i == 0)))
+
+    if rank == 0:
+        first = entries[0]
+        line = {
+            "metric": first["metric"], "value": first["value"], "unit": first["unit"], "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": first["ms_per_step"], "higher_is_better": True,
+            "scaling": first["scaling"], "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": first["config"], "bursts": first["bursts"], "roofline": first["roofline"],
+            "step_hbm": first["step_hbm"], "kernels": first["kernels"], "e2e": first["e2e"],
+            "gpu_launches": first["gpu_launches"], "clocks": first["clocks"],
+        }
+        for key in ("e2e_solve", "cpu_baseline"):
+            if key in first:
+                line[key] = first[key]
+        if check is not None:
+            line["check"] = check
+        line["workloads"] = [{k: v for k, v in e.items() if k != "kernels"} for e in entries[1:]]
         print(json.dumps(line), flush=True)
     barrier(dist)
     itf.close()
     if dist is not None:
         dist.destroy_process_group()
+    if check is not None and not check["ok_on_all_ranks"]:
+        sys.exit(1)
 
 
 def main():
@@ -393,17 +564,20 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cg", choices=["cg", "jacobi2d", "jacobi3d", "chain", "matvec"])
+    ap.add_argument("--workload", default="cg", choices=ALL_WORKLOADS,
+                    help="the workload of the top-level figures; the others follow under 'workloads'")
+    ap.add_argument("--only", action="store_true", help="measure the named workload only")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--scale", type=float, default=1.0, help="linear problem-size factor (1 = the configured size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the untimed parity check against the oracle")
     ap.add_argument("--halo", type=int, default=0, help="halo rows per side for N > 1 (0: per-workload default)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world)
         return
     run_gpu(args, rank, world, local_rank)
 

@@ -5,7 +5,7 @@ The public names mirror ``charmnumeric/__init__.py`` of the reference; ``sqrt``,
 ``libcnb200.so`` (see ``include/cnb200.h``); there is no other execution path.
 """
 from . import random  # noqa: F401
-from .context import Context, comm_unique_id, dag_check, group_compile_check  # noqa: F401
+from .context import Context, comm_unique_id, dag_check, group_compile_check, partition  # noqa: F401
 from .frontend import (  # noqa: F401
     Array, ArrayOperation, ArrayView, CharmNumericInterface, DType, LocalCluster, add, arange, array, asarray,
     copy, copyto, create_array, diag, divide, dot, dot2d, empty, empty_like, execute, exp, eye, full,

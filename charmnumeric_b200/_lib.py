@@ -45,6 +45,9 @@ SIGNATURES = {
     "cn_get": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, _P]),
     "cn_get_local": (C.c_int, [_P, C.c_int, _I64P, _I64P, C.c_int64, _P]),
     "cn_put": (C.c_int, [_P, C.c_int, C.c_int, _I64P, C.c_int, _P]),
+    "cn_get_root": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int, _P]),
+    "cn_put_local": (C.c_int, [_P, C.c_int, C.c_int, _I64P, C.c_int, C.c_int64, _P]),
+    "cn_execute_node": (C.c_int, [_P, C.c_char_p, C.c_int64]),
     "cn_delete_array": (C.c_int, [_P, C.c_int]),
     "cn_array_info": (C.c_int, [_P, C.c_int, C.POINTER(C.c_int), _I64P, C.POINTER(C.c_int),
                                 _I64P, _I64P]),

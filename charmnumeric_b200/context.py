@@ -18,6 +18,15 @@ def comm_unique_id():
     return buf.raw
 
 
+def partition(n0, nranks, rank):
+    """Rows [begin, end) of dimension 0 that ``rank`` of ``nranks`` owns (host-only)."""
+    lib = _lib.load()
+    b = C.c_int64()
+    e = C.c_int64()
+    _lib.check(None, lib.cn_partition(int(n0), int(nranks), int(rank), C.byref(b), C.byref(e)))
+    return b.value, e.value
+
+
 class Context:
     """One rank of the backend.  ``device`` is the CUDA device index of this process."""
 
@@ -99,6 +108,41 @@ class Context:
         self._check(self._lib.cn_get(self._h, out.ndim, self.epoch, int(name), out.size,
                                      WIRE_DTYPES[out.dtype], out.ctypes.data_as(C.c_void_p)))
         return out
+
+    def get_root(self, name, root=0, shape=None, dtype=None):
+        """Whole array on rank ``root`` only (numpy there, None on the other ranks); every
+        rank has to call it."""
+        if shape is None or dtype is None:
+            info = self.array_info(name)
+            shape, dtype = info["shape"], info["dtype"]
+        dtype = np.dtype(dtype)
+        count = int(np.prod(shape))
+        out = np.empty(shape, dtype=dtype) if self.rank == root else None
+        ptr = out.ctypes.data_as(C.c_void_p) if out is not None else None
+        self._check(self._lib.cn_get_root(self._h, len(shape), self.epoch, int(name), count,
+                                          WIRE_DTYPES[dtype], int(root), ptr))
+        return out
+
+    def get_local_into(self, name, out):
+        """This rank's slab into a caller-provided (e.g. pinned) contiguous numpy buffer."""
+        b = C.c_int64()
+        e = C.c_int64()
+        self._check(self._lib.cn_get_local(self._h, int(name), C.byref(b), C.byref(e), out.size,
+                                           out.ctypes.data_as(C.c_void_p)))
+        return (b.value, e.value)
+
+    def put_local(self, name, shape, slab):
+        """Upload this rank's slab of an array of global ``shape`` from a host buffer that
+        holds only those rows."""
+        slab = np.ascontiguousarray(slab)
+        cshape = (C.c_int64 * len(shape))(*shape)
+        self._check(self._lib.cn_put_local(self._h, int(name), len(shape), cshape, WIRE_DTYPES[slab.dtype],
+                                           slab.size, slab.ctypes.data_as(C.c_void_p)))
+
+    def execute_node(self, node):
+        """Run one node at once (no DAG around it)."""
+        blob = node.pack()
+        self._check(self._lib.cn_execute_node(self._h, blob, len(blob)))
 
     def get_local(self, name):
         info = self.array_info(name)

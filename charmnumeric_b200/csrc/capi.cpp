@@ -93,6 +93,25 @@ int cn_put(cn_context* ctx, int name, int ndims, const int64_t* shape, int dtype
     return ctx->impl.put(name, ndims, shape, dtype, host);
 }
 
+int cn_get_root(cn_context* ctx, int ndims, int epoch, int name, int64_t count, int dtype, int root,
+                void* out) {
+    (void)ndims;
+    (void)epoch;
+    if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.get_root(name, count, dtype, root, out);
+}
+
+int cn_put_local(cn_context* ctx, int name, int ndims, const int64_t* shape, int dtype,
+                 int64_t capacity, const void* host_slab) {
+    if (!ctx || !shape) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.put_local(name, ndims, shape, dtype, capacity, host_slab);
+}
+
+int cn_execute_node(cn_context* ctx, const char* node_blob, int64_t size) {
+    if (!ctx || !node_blob) return cn::CN_ERR_INVALID_ARGUMENT;
+    return ctx->impl.execute_single_node(node_blob, size);
+}
+
 int cn_delete_array(cn_context* ctx, int name) {
     if (!ctx) return cn::CN_ERR_INVALID_ARGUMENT;
     return ctx->impl.delete_array(name);

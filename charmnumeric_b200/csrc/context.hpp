@@ -125,6 +125,9 @@ public:
     int receive_dag(int epoch, int64_t size, const char* msg);
     int get(int name, int64_t count, int dtype, void* out);
     int get_local(int name, int64_t* row_begin, int64_t* row_end, int64_t capacity, void* out);
+    int get_root(int name, int64_t count, int dtype, int root, void* out);
+    int put_local(int name, int ndims, const int64_t* shape, int dtype, int64_t capacity, const void* host_slab);
+    int execute_single_node(const char* blob, int64_t size);
     int put(int name, int ndims, const int64_t* shape, int dtype, const void* host);
     int delete_array(int name);
     int synchronize();

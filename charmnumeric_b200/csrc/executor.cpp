@@ -1070,6 +1070,67 @@ int Context::get(int name, int64_t count, int dtype, void* out) {
     return synchronize();
 }
 
+// The whole array on rank `root` only (the reference assembles it on PE 0,
+// src/partition_get.cpp:3-67): every other rank sends its slab straight to the root, which
+// receives the slabs side by side in a device staging buffer and copies it to the host once.
+// Only the root holds the full array; NVLink carries every slab once.
+int Context::get_root(int name, int64_t count, int dtype, int root, void* out) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    if (root < 0 || root >= nranks_) return fail(CN_ERR_INVALID_ARGUMENT, "get_root: root rank out of range");
+    if (nranks_ == 1) return get(name, count, dtype, out);
+    cudaSetDevice(device_);
+    Array* x = find(name);
+    if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "get_root: unknown array " + std::to_string(name));
+    if (dtype != x->dtype) return fail(CN_ERR_BAD_DTYPE, "get_root: dtype differs from the stored array");
+    if (count != x->global_elems()) return fail(CN_ERR_SHAPE_MISMATCH, "get_root: element count differs from the stored array");
+    const bool is_root = rank_ == root;
+    if (is_root && !out) return fail(CN_ERR_INVALID_ARGUMENT, "get_root: null output buffer on the root");
+    const size_t esz = dtype_size(dtype);
+    int rc;
+    if (x->replicated) {
+        if (is_root) {
+            if ((rc = cuda_fail(cudaMemcpyAsync(out, x->buf.data, count * esz, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+            stats_.bytes_d2h += count * esz;
+        }
+        return synchronize();
+    }
+    for (int r = 0; r < nranks_; ++r)
+        if (failed_[r]) return fail(CN_ERR_RANK_FAILED, "rank " + std::to_string(r) + " was marked failed");
+    if (!comm_.ready) return fail(CN_ERR_COMM, "get across ranks needs cn_comm_init first");
+    if (is_root) {
+        if ((rc = ensure_scratch(count * esz + 256))) return rc;
+        x = find(name);
+    }
+    {
+        CommGroup group(&err_);
+        if ((rc = group.started())) return rc;
+        if (is_root) {
+            for (int p = 0; p < nranks_; ++p) {
+                int64_t b, e;
+                partition(x->shape[0], &b, &e, p);
+                if (e <= b || p == root) continue;
+                if ((rc = comm_recv(&comm_, (char*)scratch_ + b * x->unit * esz, (e - b) * x->unit, dtype, p, stream_, &err_))) return rc;
+            }
+        } else if (x->local_elems() > 0) {
+            if ((rc = comm_send(&comm_, x->buf.data, x->local_elems(), dtype, root, stream_, &err_))) return rc;
+        }
+        if ((rc = group.end())) return rc;
+    }
+    if (is_root) {
+        // the root's own slab goes straight from the array to the host buffer
+        const size_t own_off = (size_t)x->row_begin * x->unit * esz, own = (size_t)x->local_elems() * esz;
+        if (own_off)
+            if ((rc = cuda_fail(cudaMemcpyAsync(out, scratch_, own_off, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+        if (own)
+            if ((rc = cuda_fail(cudaMemcpyAsync((char*)out + own_off, x->buf.data, own, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+        const size_t tail = own_off + own;
+        if (count * esz > tail)
+            if ((rc = cuda_fail(cudaMemcpyAsync((char*)out + tail, (char*)scratch_ + tail, count * esz - tail, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+        stats_.bytes_d2h += count * esz;
+    }
+    return synchronize();
+}
+
 int Context::get_local(int name, int64_t* row_begin, int64_t* row_end, int64_t capacity, void* out) {
     if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
     cudaSetDevice(device_);
@@ -1102,6 +1163,39 @@ int Context::put(int name, int ndims, const int64_t* shape, int dtype, const voi
     }
     x->halo_fresh = 0;
     return CN_OK;
+}
+
+// This rank's slab only, from a host buffer that holds just those rows.
+int Context::put_local(int name, int ndims, const int64_t* shape, int dtype, int64_t capacity, const void* host_slab) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    cudaSetDevice(device_);
+    Array* x = nullptr;
+    int rc = create_array(name, ndims, shape, dtype, false, &x);
+    if (rc) return rc;
+    if (capacity < x->local_elems()) return fail(CN_ERR_INVALID_ARGUMENT, "put_local: buffer smaller than this rank's slab");
+    const size_t bytes = (size_t)x->local_elems() * dtype_size(dtype);
+    if (bytes) {
+        if (!host_slab) return fail(CN_ERR_INVALID_ARGUMENT, "put_local: null host buffer");
+        if ((rc = cuda_fail(cudaMemcpyAsync(x->buf.data, host_slab, bytes, cudaMemcpyHostToDevice, stream_), "put copy"))) return rc;
+        stats_.bytes_h2d += bytes;
+    }
+    x->halo_fresh = 0;
+    return CN_OK;
+}
+
+// One serialized node (the `node` production of the blob format), executed at once: the
+// executor-level entry point (DAGExecutor::execute_dag_node, src/backend.hpp:334).
+int Context::execute_single_node(const char* blob, int64_t size) {
+    if (!initialised_) return fail(CN_ERR_NO_DEVICE, "context not initialised");
+    for (int r = 0; r < nranks_; ++r)
+        if (failed_[r]) return fail(CN_ERR_RANK_FAILED, "rank " + std::to_string(r) + " was marked failed");
+    cudaSetDevice(device_);
+    Dag dag;
+    dag.nodes.emplace_back();
+    int rc = parse_node(blob, size, &dag.nodes[0], &err_);
+    if (rc) return rc;
+    size_t i = 0;
+    return execute_node(dag, &i);
 }
 
 int Context::timer_start() {

@@ -50,9 +50,28 @@ class Workload:
         self.blobs = []         # step blobs; step i uses blobs[self.pick(i)]
         self.nodes = []         # the node lists behind the blobs (for the oracle in tests)
         self.result = None      # size-1 array read back per step in the end-to-end leg
-        self.points = 0         # grid points / elements / matrix entries per step (all ranks)
-        self.bytes_per_step = 0  # algorithmic HBM bytes per step, all ranks
-        self.description = ""
+        d = self.describe(nranks, scale)
+        self.shape = d["shape"]
+        self.points = d["points"]                  # grid points / elements / matrix entries per step (all ranks)
+        self.bytes_per_step = d["bytes_per_step"]  # algorithmic HBM bytes per step, all ranks
+        self.description = d["description"]
+
+    @classmethod
+    def describe(cls, nranks=1, scale=1.0):
+        """Shape, size and description of the workload; needs no GPU (the CPU arm of the
+        benchmark reports the same configuration string)."""
+        raise NotImplementedError
+
+    def release(self):
+        """Drop every array of the workload and let the backend free them."""
+        import gc
+        self.keep = []
+        self.result = None
+        for key, value in list(vars(self).items()):
+            if isinstance(value, (F.Array, F.ArrayView)):
+                setattr(self, key, None)
+        gc.collect()
+        F.execute(self.itf)
 
     def pick(self, step_index):
         return 0
@@ -75,16 +94,17 @@ class CG(Workload):
     name = "cg"
     metric = "cg_iterations_per_sec"
 
-    def __init__(self, interface, nranks=1, scale=1.0):
-        super().__init__(interface, nranks, scale)
+    @classmethod
+    def describe(cls, nranks=1, scale=1.0):
         n = max(8, int(8192 * scale))
         m0, m1 = n * nranks + 2, n + 2
-        self.shape = (m0, m1)
-        self.points = (m0 - 2) * (m1 - 2)
-        self.bytes_per_step = 88 * n * n * nranks
-        self.description = (f"C3 matrix-free CG, 2-D Poisson 5-point, {n}x{n} unknowns per GPU "
-                            f"(global {m0 - 2}x{m1 - 2}), one stencil matvec + two dots + three "
-                            "axpys per iteration, slab decomposition")
+        return {"shape": (m0, m1), "points": (m0 - 2) * (m1 - 2), "bytes_per_step": 88 * n * n * nranks,
+                "description": (f"C3 matrix-free CG, 2-D Poisson 5-point, {n}x{n} unknowns per GPU "
+                                f"(global {m0 - 2}x{m1 - 2}), one stencil matvec + two dots + three "
+                                "axpys per iteration, slab decomposition")}
+
+    def __init__(self, interface, nranks=1, scale=1.0):
+        super().__init__(interface, nranks, scale)
         b = F.zeros(self.shape)
         b[1:-1, 1:-1] = F.uniform(self.shape, seed=SEED + 3)[1:-1, 1:-1]
         x = F.zeros(self.shape)
@@ -111,20 +131,33 @@ class CG(Workload):
             self.keep += [pAp, alpha, rtr_new, beta]
         self.add_step(step)
 
+        # start of a solve from a right-hand side that is already in `b` (uploaded with
+        # cn_put / cn_put_local): x = 0, r = p = b, rtr = r.r
+        def init():
+            x[...] = 0.0
+            r[...] = b
+            p[...] = b
+            t = F.dot2d(r, r)
+            rtr[...] = t
+            self.keep.append(t)
+        self.init_blob = wire.dag_blob(_capture_step(init))
+
 
 class Jacobi2D(Workload):
     name = "jacobi2d"
     metric = "jacobi2d_iterations_per_sec"
 
+    @classmethod
+    def describe(cls, nranks=1, scale=1.0):
+        n = max(8, int(2048 * scale))
+        shape = (n * nranks, n)
+        return {"shape": shape, "points": shape[0] * n, "bytes_per_step": 16 * shape[0] * n,
+                "description": (f"C1 Jacobi2D 5-point, {n}x{n} per GPU (global {shape[0]}x{n}), "
+                                "residual sum((new-old)^2) every 10 iterations")}
+
     def __init__(self, interface, nranks=1, scale=1.0, res_every=10):
         super().__init__(interface, nranks, scale)
-        n = max(8, int(2048 * scale))
-        self.shape = (n * nranks, n)
         self.res_every = res_every
-        self.points = self.shape[0] * self.shape[1]
-        self.bytes_per_step = 16 * self.points
-        self.description = (f"C1 Jacobi2D 5-point, {n}x{n} per GPU (global {self.shape[0]}x{n}), "
-                            f"residual sum((new-old)^2) every {res_every} iterations")
         u = F.uniform(self.shape, seed=SEED + 1)
         u[0, :] = 1.0
         u[-1, :] = 0.0
@@ -159,15 +192,17 @@ class Jacobi3D(Workload):
     name = "jacobi3d"
     metric = "jacobi3d_iterations_per_sec"
 
+    @classmethod
+    def describe(cls, nranks=1, scale=1.0):
+        n = max(8, int(1024 * scale))
+        shape = (n * nranks, n, n)
+        return {"shape": shape, "points": shape[0] * n * n, "bytes_per_step": 16 * shape[0] * n * n,
+                "description": (f"C5 Jacobi3D 7-point, {n}^3 per GPU (global {shape[0]}x{n}x{n}), "
+                                "z-slab decomposition, residual every 10 iterations")}
+
     def __init__(self, interface, nranks=1, scale=1.0, res_every=10):
         super().__init__(interface, nranks, scale)
-        n = max(8, int(1024 * scale))
-        self.shape = (n * nranks, n, n)
         self.res_every = res_every
-        self.points = self.shape[0] * n * n
-        self.bytes_per_step = 16 * self.points
-        self.description = (f"C5 Jacobi3D 7-point, {n}^3 per GPU (global {self.shape[0]}x{n}x{n}), "
-                            f"z-slab decomposition, residual every {res_every} iterations")
         u = F.uniform(self.shape, seed=SEED + 5)
         u[0, :, :] = 1.0
         u[-1, :, :] = 0.0
@@ -211,14 +246,16 @@ class Chain(Workload):
     unit = "repeats/s"
     scaling = "strong"
 
+    @classmethod
+    def describe(cls, nranks=1, scale=1.0):
+        n = max(8, int((1 << 28) * scale))
+        return {"shape": (n,), "points": n, "bytes_per_step": 16 * n,
+                "description": (f"C2 fused chain + sum, two float64 vectors of length {n} in total, "
+                                "one fused kernel and one scalar result per repeat")}
+
     def __init__(self, interface, nranks=1, scale=1.0):
         super().__init__(interface, nranks, scale)
-        n = max(8, int((1 << 28) * scale))
-        self.shape = (n,)
-        self.points = n
-        self.bytes_per_step = 16 * n
-        self.description = (f"C2 fused chain + sum, two float64 vectors of length {n} in total, "
-                            "one fused kernel and one scalar result per repeat")
+        n = self.shape[0]
         a = F.uniform((n,), seed=SEED + 2, low=-1.0, high=1.0)
         b = F.uniform((n,), seed=SEED + 22, low=-1.0, high=1.0)
         F.execute(interface)
@@ -238,14 +275,16 @@ class Matvec(Workload):
     unit = "steps/s"
     scaling = "strong"
 
+    @classmethod
+    def describe(cls, nranks=1, scale=1.0):
+        n = max(8, int(65536 * scale))
+        return {"shape": (n, n), "points": n * n, "bytes_per_step": 8 * n * n + 3 * 8 * n,
+                "description": (f"C4 dense row-partitioned matvec, A {n}x{n} float64, power iteration "
+                                "y = A x; x = y / sqrt(y.y)")}
+
     def __init__(self, interface, nranks=1, scale=1.0):
         super().__init__(interface, nranks, scale)
-        n = max(8, int(65536 * scale))
-        self.shape = (n, n)
-        self.points = n * n
-        self.bytes_per_step = 8 * n * n + 3 * 8 * n
-        self.description = (f"C4 dense row-partitioned matvec, A {n}x{n} float64, power iteration "
-                            "y = A x; x = y / sqrt(y.y)")
+        n = self.shape[0]
         A = F.uniform((n, n), seed=SEED + 4, low=-1.0 / 256, high=1.0 / 256)
         x = F.uniform((n,), seed=SEED + 44, low=-1.0, high=1.0)
         F.execute(interface)

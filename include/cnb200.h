@@ -83,6 +83,13 @@ int cn_receive_dag(cn_context* ctx, int epoch, int64_t size, const char* msg);
  * send_reply (src/backend.ci:16-17, src/dag_group_runtime.cpp:55-118,
  * src/partition_get.cpp:3-67).  Waits for all enqueued work. */
 int cn_get(cn_context* ctx, int ndims, int epoch, int name, int64_t count, int dtype, void* out);
+/* The same gather onto ONE rank, as the reference does it (process_get sends every tile to
+ * PE 0, which replies to the client: src/partition_get.cpp:3-67,
+ * src/dag_group_runtime.cpp:99-118).  Every rank calls it; only `root` receives the array
+ * (`out` may be NULL elsewhere): the other ranks send their slab to the root and hold no copy
+ * of the whole array, on the device or on the host. */
+int cn_get_root(cn_context* ctx, int ndims, int epoch, int name, int64_t count, int dtype,
+                int root, void* out);
 /* This rank's slab only (rows [*row_begin, *row_end) of dimension 0); out may be NULL to
  * query the range.  No counterpart in the reference (its chares are gathered on PE 0). */
 int cn_get_local(cn_context* ctx, int name, int64_t* row_begin, int64_t* row_end,
@@ -92,6 +99,20 @@ int cn_get_local(cn_context* ctx, int name, int64_t* row_begin, int64_t* row_end
  * (charmnumeric/charmnumeric.py:863-878). */
 int cn_put(cn_context* ctx, int name, int ndims, const int64_t* shape, int dtype,
            const void* host);
+
+/* The slab-wise counterpart of cn_put: `host_slab` holds only the rows this rank owns
+ * (cn_partition of shape[0]), `capacity` its length in elements.  No counterpart in the
+ * reference. */
+int cn_put_local(cn_context* ctx, int name, int ndims, const int64_t* shape, int dtype,
+                 int64_t capacity, const void* host_slab);
+
+/* Execute one DAG node at once.  Stands in for DAGExecutor::execute_dag_node(DAGNode*)
+ * (src/backend.hpp:322-347, src/executor_core.cpp:194), which the reference's scheduler calls
+ * once per ready node on every chare; `node_blob` is one `node` production of the CNB1 format
+ * (what cn_compile_group takes).  Completion is stream-ordered (the reference reports
+ * node_finished(node_id)); the status code is the result.  A one-node cn_receive_dag does
+ * the same work plus the plan cache and the delete list. */
+int cn_execute_node(cn_context* ctx, const char* node_blob, int64_t size);
 
 /* DAGExecutor::delete_array(int name) (src/backend.hpp:334, src/executor_core.cpp:184-192). */
 int cn_delete_array(cn_context* ctx, int name);

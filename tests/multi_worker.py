@@ -92,6 +92,19 @@ def main():
     for k, v in outs.items():
         result["gpu_" + k] = itf.context.get(v.name).reshape(v.shape)
         result["cpu_" + k] = np.array(orc.get(v.name)).reshape(v.shape)
+    if case == "matvec":
+        # the root-only gather: rank 1 receives the array, every other rank gets nothing
+        y = outs["y"]
+        rooted = itf.context.get_root(y.name, root=1)
+        assert (rooted is not None) == (rank == 1)
+        if rank == 1:
+            assert rooted.tobytes() == result["gpu_y"].tobytes()
+        # slab-wise upload: every rank hands in only its own rows
+        rng = np.random.default_rng(5)
+        whole = rng.uniform(-1.0, 1.0, (301, 7))
+        b, e = cnp.partition(301, nranks, rank)
+        itf.context.put_local(999001, whole.shape, whole[b:e])
+        assert itf.context.get(999001).tobytes() == whole.tobytes()
     st = itf.context.stats()
     result["halo_exchanges"] = np.array(st["halo_exchanges"])
     result["allreduces"] = np.array(st["allreduces"])
