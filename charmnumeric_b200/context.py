@@ -217,6 +217,21 @@ def group_compile_check(node):
     return src.value.decode(), nb.value
 
 
+def fuse_check(node_a, node_b):
+    """Host-only: the CUDA source of the single kernel that runs ``node_a`` (a whole-array
+    assignment) and ``node_b`` (a stencil over the assigned array), or None when the pair does
+    not fuse."""
+    lib = _lib.load()
+    a, b = node_a.pack(), node_b.pack()
+    src = C.create_string_buffer(1 << 18)
+    err = C.create_string_buffer(1 << 14)
+    fused = C.c_int(0)
+    status = lib.cn_fuse_check(a, len(a), b, len(b), src, len(src), C.byref(fused), err, len(err))
+    if status != 0:
+        raise _lib.CnError(status, err.value.decode())
+    return src.value.decode() if fused.value else None
+
+
 def dag_check(blob):
     """Host-only: parse a DAG blob; returns (n_nodes, n_roots)."""
     lib = _lib.load()

@@ -196,13 +196,67 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
         tile.tx = 64;
         tile.r = 4;
     }
-    if (const char* pf = getenv("CN_FLAT_PREFETCH")) tile.prefetch = g.flat && atoi(pf) != 0;
+    if (const char* sh = getenv("CN_STENCIL_SHFL")) tile.shfl = atoi(sh) != 0 && !g.flat && !g.staged;
+    if (const char* pf = getenv("CN_FLAT_PREFETCH")) tile.prefetch = g.flat ? std::max(0, std::min(2, atoi(pf))) : 0;
     rc = cn::nvrtc_compile(src, tile, &cubin, &log);
     if (rc) {
         copy_err(log, err, errcap);
         return rc;
     }
     if (cubin_bytes) *cubin_bytes = (int64_t)cubin.size();
+    return cn::CN_OK;
+}
+
+int cn_fuse_check(const char* node_a, int64_t size_a, const char* node_b, int64_t size_b, char* source,
+                  int64_t cap, int* fused, char* err, int errcap) {
+    if (fused) *fused = 0;
+    cn::DagNode a, b, m;
+    std::string e;
+    int rc = cn::parse_node(node_a, size_a, &a, &e);
+    if (!rc) rc = cn::parse_node(node_b, size_b, &b, &e);
+    if (rc) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    cn::GroupIR g;
+    cn::DagNode cons, prod;
+    int pseudo = 0, target = 0;
+    bool staged = false;
+    if (!(getenv("CN_FUSE_PRODUCERS") && atoi(getenv("CN_FUSE_PRODUCERS")) < 2) &&
+        cn::stage_producer(a, b, &cons, &prod, &pseudo, &target))
+        staged = cn::lower_staged_producer(cons, prod, pseudo, target, {}, &g, &e) == cn::CN_OK;
+    if (!staged && getenv("CN_DEBUG_FUSE")) fprintf(stderr, "[cnb200] staged form not used: %s\n", e.c_str());
+    if (!staged) {
+        if (!cn::inline_producer(a, b, &m)) return cn::CN_OK;
+        g = cn::GroupIR();
+        rc = cn::lower_group(m, {}, &g, &e);
+        if (rc || g.cls != cn::GroupIR::SHIFTED || g.flat) {
+            copy_err(e, err, errcap);
+            return cn::CN_OK;  // the pair would run as two kernels
+        }
+    }
+    std::string src;
+    if ((rc = cn::generate_source(g, &src, &e))) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    std::vector<char> cubin;
+    std::string log;
+    cn::TileConfig tile;
+    if (g.staged) {
+        tile.tx = 64;
+        tile.r = g.producer.empty() ? 4 : 8;
+    }
+    if ((rc = cn::nvrtc_compile(src, tile, &cubin, &log))) {
+        copy_err(log, err, errcap);
+        return rc;
+    }
+    if (source && cap > 0) {
+        size_t n = std::min<size_t>(src.size(), (size_t)cap - 1);
+        memcpy(source, src.data(), n);
+        source[n] = 0;
+    }
+    if (fused) *fused = 1;
     return cn::CN_OK;
 }
 
@@ -244,6 +298,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->peer_exchanges = s.peer_exchanges;
     out->overlapped_sweeps = s.overlapped_sweeps;
     out->deep_halo_sweeps = s.deep_halo_sweeps;
+    out->inlined_producers = s.inlined_producers;
     return cn::CN_OK;
 }
 
@@ -271,10 +326,16 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         return ctx->impl.debug_peer_wait();
     } else if (k == "p2p") {
         ctx->impl.set_p2p(value != 0);
+    } else if (k == "fuse_producers") {
+        if (value < 0 || value > 2) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_fuse_producers((int)value);
+    } else if (k == "stencil_shfl") {
+        ctx->impl.set_stencil_shfl(value != 0);
     } else if (k == "plan_cache") {
         ctx->impl.set_plan_cache(value != 0);
     } else if (k == "flat_prefetch") {
-        ctx->impl.set_flat_prefetch(value != 0);
+        if (value < -1 || value > 2) return cn::CN_ERR_INVALID_ARGUMENT;
+        ctx->impl.set_flat_prefetch((int)value);
     } else if (k == "profile") {
         ctx->impl.set_profile(value != 0);
     } else if (k == "fuse_reductions") {

@@ -38,12 +38,12 @@ struct Gen {
     std::string val(const ValRef& v, int e) const {
         std::ostringstream s;
         switch (v.kind) {
-            case ValRef::LEAF: s << "l" << v.idx << "_" << e; break;
-            case ValRef::CONST: s << "c" << v.idx; break;
-            case ValRef::BCAST: s << "b" << v.idx; break;
+            case ValRef::LEAF: s << pfx << "l" << v.idx << "_" << e; break;
+            case ValRef::CONST: s << pfx << "c" << v.idx; break;
+            case ValRef::BCAST: s << pfx << "b" << v.idx; break;
             case ValRef::ROOT:
-                if (g.roots[v.idx].domain == DOM_SCALAR) s << "r" << v.idx;
-                else s << "r" << v.idx << "_" << e;
+                if (g.roots[v.idx].domain == DOM_SCALAR) s << pfx << "r" << v.idx;
+                else s << pfx << "r" << v.idx << "_" << e;
                 break;
             case ValRef::OUTVAL: s << "w" << v.idx << "_" << e; break;
             default: s << "(T)0";
@@ -71,6 +71,7 @@ struct Gen {
         return "(T)0";
     }
 
+    std::string pfx;           // name prefix of this group's values (a staged producer's are "P...")
     bool staged_mode = false;  // stencil array comes from the shared-memory ring
     bool fast_loads = false;   // inside a row-interior tile: every load is unconditional
     bool carry_mode = false;   // staged 3-D march: the thread's own column is carried in registers
@@ -100,7 +101,7 @@ struct Gen {
         o << "typedef " << type_name(g.dtype) << " T;\n";
         o << "typedef " << (is_float() ? "double" : "long long") << " ACC;\n";
         if (g.vec == 2) o << "typedef " << (g.dtype == DT_I64 ? "longlong2" : "double2") << " T2;\n";
-        o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK) " << g.entry_name() << "("
+        o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK, CN_MINB) " << g.entry_name() << "("
              "const __grid_constant__ CnGroupArgs a) {\n";
         for (size_t i = 0; i < g.scalars.size(); ++i)
             o << "  const T c" << i << " = (T)a.sc[" << i << "];\n";
@@ -245,6 +246,7 @@ struct Gen {
                         done.insert(c);
                     }
             }
+            // 128-bit pair loads first, so that single neighbours can be taken from them
             for (int64_t c : row.cols) {
                 if (done.count(c)) continue;
                 bool even = ((c % 2) + 2) % 2 == 0;
@@ -254,11 +256,40 @@ struct Gen {
                       << " = q.y; }\n";
                     done.insert(c);
                     done.insert(c + 1);
-                } else {
-                    o << ind << "  " << colname((int)r, c) << " = *(" << base.str() << " + (" << c
-                      << "LL));\n";
-                    done.insert(c);
                 }
+            }
+            // In a row-interior tile the lanes of a warp hold consecutive pairs of one row: the
+            // elements just left and right of a thread's own pair sit in its neighbour lanes'
+            // registers.  A shuffle fetches them; only the warp's edge lanes still load.
+            const bool can_shfl = fast_loads && !smem && V == 2 && N >= 2 && row.cols.count(0) &&
+                                  row.cols.count(1) && done.count(0) && done.count(1);
+            bool shfl_open = false;
+            if (can_shfl) {
+                for (int64_t c : row.cols) {
+                    if (done.count(c) || c < -2 || c > 3) continue;
+                    if (!shfl_open) o << "#if CN_SHFL && (CN_TX % 32) == 0\n";
+                    shfl_open = true;
+                    const bool up = c < 0;
+                    o << ind << "  " << colname((int)r, c) << " = __shfl_" << (up ? "up" : "down") << "_sync(wm, "
+                      << colname((int)r, up ? c + 2 : c - 2) << ", 1);\n";
+                    o << ind << "  if (" << (up ? "lane == 0" : "(lane == 31) | (x + 2 >= xhi)") << ") "
+                      << colname((int)r, c) << " = *(" << base.str() << " + (" << c << "LL));\n";
+                }
+                if (shfl_open) {
+                    o << "#else\n";
+                    for (int64_t c : row.cols) {
+                        if (done.count(c) || c < -2 || c > 3) continue;
+                        o << ind << "  " << colname((int)r, c) << " = *(" << base.str() << " + (" << c << "LL));\n";
+                    }
+                    o << "#endif\n";
+                    for (int64_t c : row.cols)
+                        if (c >= -2 && c <= 3) done.insert(c);
+                }
+            }
+            for (int64_t c : row.cols) {
+                if (done.count(c)) continue;
+                o << ind << "  " << colname((int)r, c) << " = *(" << base.str() << " + (" << c << "LL));\n";
+                done.insert(c);
             }
             o << ind << "}\n";
         }
@@ -442,7 +473,15 @@ struct Gen {
             }
             emit_guards(fast);
             if (fast && N == 1) o << "      {\n";
-            else if (fast) o << "      if (x < xhi) {\n";
+            else if (fast) {
+                // all lanes of the warp are here (the tile is interior for the whole block):
+                // the lanes that go on form a prefix of the warp
+                o << "#if CN_SHFL && (CN_TX % 32) == 0\n";
+                o << "      const unsigned int wm = __ballot_sync(0xffffffffu, x < xhi);\n";
+                o << "      const int lane = threadIdx.x & 31;\n";
+                o << "#endif\n";
+                o << "      if (x < xhi) {\n";
+            }
             else o << "      if " << guard_any(DOM_BOX) << " {\n";
             fast_loads = fast;
             shifted_body("        ");
@@ -462,7 +501,7 @@ struct Gen {
             }
         const bool prefetch = g.flat && V == 2 && !flat_rows.empty();
         if (prefetch) {
-            o << "#if CN_PREFETCH\n  bool have = false;\n";
+            o << "#if CN_PREFETCH == 1\n  bool have = false;\n";
             for (size_t k = 0; k < flat_rows.size(); ++k) o << "  T2 nx" << k << "[CN_R] = {};\n";
             o << "#endif\n";
         }
@@ -509,6 +548,7 @@ struct Gen {
             };
             o << "#if CN_PREFETCH\n";
             for (size_t k = 0; k < flat_rows.size(); ++k) o << "      T2 cu" << k << "[CN_R];\n";
+            o << "#if CN_PREFETCH == 1\n";
             o << "      if (have) {\n#pragma unroll\n        for (int r = 0; r < CN_R; ++r) {";
             for (size_t k = 0; k < flat_rows.size(); ++k) o << " cu" << k << "[r] = nx" << k << "[r];";
             o << " }\n      } else {\n";
@@ -520,6 +560,10 @@ struct Gen {
             o << "      if (have) {\n";
             load_all("nx", "n0");
             o << "      }\n";
+            o << "#else\n";
+            // every load of the tile ahead of its arithmetic
+            load_all("cu", "t0");
+            o << "#endif\n";
             pref_mode = true;
             emit_rows(true);
             pref_mode = false;
@@ -530,12 +574,84 @@ struct Gen {
             emit_rows(true);
         }
         o << "    } else {\n";
-        if (prefetch) o << "#if CN_PREFETCH\n      have = false;\n#endif\n";
+        if (prefetch) o << "#if CN_PREFETCH == 1\n      have = false;\n#endif\n";
         emit_rows(false);
         o << "    }\n";
         o << "  }\n";
         red_epilogue();
         o << "}\n";
+    }
+
+    // ---- staged producer: constants and inputs of the flat group that fills the tiles ------
+    void producer_prologue() {
+        const GroupIR& P = g.producer[0];
+        Gen pg{P, {}, {}};
+        pg.pfx = "P";
+        const size_t sc_base = g.scalars.size(), bc_base = g.bcast_names.size();
+        for (auto& l : g.leaves) in_slot(l.name);
+        const size_t in_base = in_names.size();
+        for (size_t i = 0; i < P.scalars.size(); ++i)
+            o << "  const T Pc" << i << " = (T)a.sc[" << (sc_base + i) << "];\n";
+        for (size_t i = 0; i < P.bcast_names.size(); ++i)
+            o << "  const T Pb" << i << " = *(const T*)a.bc[" << (bc_base + i) << "];\n";
+        for (size_t i = 0; i < P.roots.size(); ++i) {
+            const RootIR& r = P.roots[i];
+            if (r.domain != DOM_SCALAR) continue;
+            o << "  const T Pr" << i << " = " << pg.expr(r.opcode, pg.val(r.a, 0), pg.val(r.b, 0)) << ";\n";
+        }
+        const std::vector<int> pin = P.input_arrays();
+        for (size_t k = 0; k < pin.size(); ++k)
+            o << "  const T* __restrict__ Pin" << k << " = (const T*)a.in[" << (in_base + k) << "];\n";
+    }
+
+    // One pass of the block over the tile's (rows + 2 hy) x (cols + 4) points, two adjacent
+    // points per thread and step: load the producer's inputs there, evaluate its roots in
+    // their own order (each a separately rounded statement, as everywhere), store the pair.
+    // Points outside the arrays get zeros; no valid stencil point reads them.
+    void producer_fill() {
+        const GroupIR& P = g.producer[0];
+        Gen pg{P, {}, {}};
+        pg.pfx = "P";
+        const std::vector<int> pin = P.input_arrays();
+        // CN_FILL_U points' loads are issued together before any of them is used
+        o << "    enum { CN_FILL_N = CN_SH * (CN_SW / 2), CN_FILL_IT = (CN_FILL_N + CN_BLOCK - 1) / CN_BLOCK };\n";
+        o << "    for (int it0 = 0; it0 < CN_FILL_IT; it0 += CN_FILL_U) {\n";
+        o << "      bool fin[CN_FILL_U];\n";
+        for (size_t k = 0; k < pin.size(); ++k) o << "      T2 Pq" << k << "[CN_FILL_U];\n";
+        o << "#pragma unroll\n";
+        o << "      for (int u = 0; u < CN_FILL_U; ++u) {\n";
+        o << "        const int i = threadIdx.x + (it0 + u) * CN_BLOCK;\n";
+        o << "        const int sy = i / (CN_SW / 2), sx = i - sy * (CN_SW / 2);\n";
+        o << "        const long long gy = ty0 - CN_HY + sy, gx = tx0 - 2 + 2 * sx;\n";
+        o << "        fin[u] = (i < CN_FILL_N) & (gy >= fy0) & (gy < fy1) & (gx >= 0) & (gx < fx1);\n";
+        o << "        const long long pp = gy * s0 + gx;\n";
+        for (size_t k = 0; k < pin.size(); ++k) {
+            o << "        Pq" << k << "[u].x = (T)0; Pq" << k << "[u].y = (T)0;\n";
+            o << "        if (fin[u]) Pq" << k << "[u] = *(const T2*)(Pin" << k << " + pp);\n";
+        }
+        o << "      }\n";
+        o << "#pragma unroll\n";
+        o << "      for (int u = 0; u < CN_FILL_U; ++u) {\n";
+        o << "        const int i = threadIdx.x + (it0 + u) * CN_BLOCK;\n";
+        o << "        const int sy = i / (CN_SW / 2), sx = i - sy * (CN_SW / 2);\n";
+        for (size_t k = 0; k < P.leaves.size(); ++k) {
+            size_t slot = 0;
+            for (size_t q = 0; q < pin.size(); ++q)
+                if (pin[q] == P.leaves[k].name) slot = q;
+            o << "        const T Pl" << k << "_0 = Pq" << slot << "[u].x, Pl" << k << "_1 = Pq" << slot << "[u].y;\n";
+        }
+        for (size_t i = 0; i < P.roots.size(); ++i) {
+            const RootIR& r = P.roots[i];
+            if (r.domain == DOM_SCALAR) continue;
+            for (int e = 0; e < 2; ++e)
+                o << "        const T Pr" << i << "_" << e << " = " << pg.expr(r.opcode, pg.val(r.a, e), pg.val(r.b, e))
+                  << ";\n";
+        }
+        o << "        T2 v; v.x = fin[u] ? " << pg.val(P.outs[0].value, 0) << " : (T)0; v.y = fin[u] ? "
+          << pg.val(P.outs[0].value, 1) << " : (T)0;\n";
+        o << "        if (i < CN_FILL_N) *(T2*)(ring + sy * CN_SW + 2 * sx) = v;\n";
+        o << "      }\n";
+        o << "    }\n";
     }
 
     // ---- SHIFTED class, staged variant -----------------------------------------------------
@@ -568,19 +684,25 @@ struct Gen {
         }
         red_decl();
         const int L = N - 1;
-        const int NS = N == 3 ? 2 * g.hz + 3 : 3;
+        const bool prod = !g.producer.empty();  // tiles are computed, not copied (2-D only)
+        const int NS = prod ? 1 : (N == 3 ? 2 * g.hz + 3 : 3);
         carry_mode = N == 3 && g.hz == 1;
+        if (prod) producer_prologue();
         o << "  enum { CN_HY = " << g.hy << ", CN_HZ = " << g.hz << ", CN_NS = CN_NS_OVERRIDE ? CN_NS_OVERRIDE : " << NS
           << ", CN_TXE = CN_TX * 2, CN_SW = CN_TXE + 4, CN_TYT = (CN_BLOCK / CN_TX) * CN_R, "
              "CN_SH = CN_TYT + 2 * CN_HY, CN_BOX = CN_SH * CN_SW, CN_SLOT = (CN_BOX + 15) / 16 * 16 };\n";
         o << "  extern __shared__ __align__(128) unsigned char cn_dyn[];\n";
         o << "  T* const ring = (T*)cn_dyn;\n";
         o << "  unsigned long long* const full = (unsigned long long*)(cn_dyn + (size_t)CN_NS * CN_SLOT * sizeof(T));\n";
-        o << "  if (threadIdx.x == 0) {\n";
-        o << "    for (int s = 0; s < CN_NS; ++s) cn_mbar_init(&full[s], 1u);\n";
-        o << "    cn_mbar_init_fence();\n";
-        o << "  }\n";
-        o << "  __syncthreads();\n";
+        if (!prod) {
+            o << "  if (threadIdx.x == 0) {\n";
+            o << "    for (int s = 0; s < CN_NS; ++s) cn_mbar_init(&full[s], 1u);\n";
+            o << "    cn_mbar_init_fence();\n";
+            o << "  }\n";
+            o << "  __syncthreads();\n";
+        } else {
+            o << "  (void)full;\n";
+        }
         o << "  const long long s0 = CN_S0 ? CN_S0 : a.stride[0];\n";
         if (N == 3) o << "  const long long s1 = CN_S1 ? CN_S1 : a.stride[1];\n";
         o << "  const long long xlo = a.lo[" << L << "], xhi = a.hi[" << L << "];\n";
@@ -651,7 +773,25 @@ struct Gen {
             o << "      }\n";
         };
 
-        if (N == 2) {
+        if (N == 2 && prod) {
+            // every tile: all threads compute the stand-in's values for the tile and its halo
+            // ring into shared memory, then the stencil reads them from there
+            o << "  const long long fy0 = a.fill_lo[0], fy1 = a.fill_hi[0], fx1 = a.fill_hi[1];\n";
+            o << "  for (unsigned int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+            o << "    const unsigned int tx = tile % ntx, ty = tile / ntx;\n";
+            o << "    const long long tx0 = xbase + (long long)tx * CN_TXE;\n";
+            o << "    const long long ty0 = a.lo[0] + (long long)ty * CN_TYT;\n";
+            o << "    __syncthreads();  // the previous tile's readers are done with the ring\n";
+            producer_fill();
+            o << "    __syncthreads();\n";
+            o << "    {\n";
+            o << "      const T* const sp0 = ring;\n";
+            o << "      const long long x = tx0 + lx * 2;\n";
+            o << "      const long long ybase = ty0 + ly * CN_R;\n";
+            emit_interior();
+            o << "    }\n";
+            o << "  }\n";
+        } else if (N == 2) {
             // tile k of this block: index blockIdx.x + k * gridDim.x, slot k % CN_NS
             o << "  const unsigned int nmine = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;\n";
             o << "  auto issue = [&](unsigned int k) {\n";

@@ -27,7 +27,9 @@ Context::Context(int device, int rank, int nranks)
         }
     }
     if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
-    if (const char* f = getenv("CN_FLAT_PREFETCH")) flat_prefetch_ = atoi(f) != 0;
+    if (const char* f = getenv("CN_FLAT_PREFETCH")) flat_prefetch_ = std::max(-1, std::min(2, atoi(f)));
+    if (const char* f = getenv("CN_FUSE_PRODUCERS")) fuse_producers_ = std::max(0, std::min(2, atoi(f)));
+    if (const char* f = getenv("CN_STENCIL_SHFL")) stencil_shfl_ = atoi(f) != 0;
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
     if (const char* f = getenv("CN_OVERLAP_HALO")) overlap_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_DEEP_HALO")) deep_halo_ = atoi(f) != 0;
@@ -621,18 +623,11 @@ int Context::execute_node(const Dag& dag, size_t* index) {
         return CN_OK;
     }
     if (is_group_node(node)) {
-        bool done = false;
-        int rc = try_plain_fill(node, &done);
-        if (rc) return rc;
-        if (done) {
-            ++*index;
-            return CN_OK;
-        }
-        // REDUCE / SUM nodes that directly follow may be folded into this group's kernel
-        std::vector<const AstNode*> fused;
-        size_t j = *index + 1;
-        if (fuse_reductions_) {
-            while (j < dag.nodes.size() && (int)fused.size() < CN_MAX_RED) {
+        // REDUCE / SUM nodes that directly follow a group may be folded into its kernel
+        auto scan_reductions = [&](size_t from, size_t* end) {
+            std::vector<const AstNode*> found;
+            size_t j = from;
+            while (fuse_reductions_ && j < dag.nodes.size() && (int)found.size() < CN_MAX_RED) {
                 const DagNode& nx = dag.nodes[j];
                 if (nx.roots.size() != 1) break;
                 const AstNode* r = nx.roots[0].get();
@@ -641,37 +636,90 @@ int Context::execute_node(const Dag& dag, size_t* index) {
                 for (auto& op : r->operands)
                     if (op.is_ref || !op.leaf || op.leaf->is_scalar) ok = false;
                 if (!ok) break;
-                fused.push_back(r);
+                found.push_back(r);
                 ++j;
             }
-        }
+            *end = j;
+            return found;
+        };
+        // A whole-array assignment followed by a stencil over the array it assigns runs as one
+        // kernel: staged (the assigned values are computed tile by tile in shared memory) where
+        // that form fits, otherwise recomputed at every stencil point.
+        DagNode merged, consumer, producer;
+        const DagNode* gnode = &node;
+        size_t after = *index + 1;
         GroupIR probe;
         bool lowered = false;
-        if (!fused.empty()) {
-            std::string perr;
-            int lrc = lower_group(node, fused, &probe, &perr);
-            bool related = false;
-            if (lrc == CN_OK && probe.cls == GroupIR::SHIFTED) {
-                // only worth fusing when a reduction operand is produced or read by the group
-                for (auto& rd : probe.reds)
-                    for (const ValRef* v : {&rd.a, &rd.b}) {
-                        if (v->kind == ValRef::OUTVAL || v->kind == ValRef::ROOT) related = true;
-                        if (v->kind == ValRef::LEAF)
-                            for (auto& l : probe.leaves)
-                                if (&l != &probe.leaves[v->idx] && l.name == probe.leaves[v->idx].name)
-                                    related = true;
-                    }
+        std::vector<const AstNode*> fused;
+        size_t j = after;
+        int rc = CN_OK;
+        if (fuse_producers_ > 0 && after < dag.nodes.size() && is_group_node(dag.nodes[after])) {
+            int pseudo = 0, target = 0;
+            if (fuse_producers_ >= 2 && stage_producer(node, dag.nodes[after], &consumer, &producer, &pseudo, &target)) {
+                size_t end = after + 1;
+                std::vector<const AstNode*> behind = scan_reductions(after + 1, &end);
+                std::string terr;
+                if (lower_staged_producer(consumer, producer, pseudo, target, behind, &probe, &terr) == CN_OK) {
+                    lowered = true;
+                    fused = behind;
+                    j = end;
+                } else if (!behind.empty() &&
+                           lower_staged_producer(consumer, producer, pseudo, target, {}, &probe, &terr) == CN_OK) {
+                    lowered = true;
+                    j = after + 1;
+                }
+                if (lowered) {
+                    gnode = &consumer;
+                    stats_.nodes++;
+                    stats_.inlined_producers++;
+                }
             }
-            if (lrc != CN_OK || probe.cls != GroupIR::SHIFTED || !related) {
-                fused.clear();
-                j = *index + 1;
-            } else {
-                lowered = true;  // the probe is the group as it will run
+            if (!lowered && inline_producer(node, dag.nodes[after], &merged)) {
+                GroupIR trial;
+                std::string terr;
+                if (lower_group(merged, {}, &trial, &terr) == CN_OK && trial.cls == GroupIR::SHIFTED && !trial.flat) {
+                    gnode = &merged;
+                    ++after;
+                    stats_.nodes++;
+                    stats_.inlined_producers++;
+                }
             }
         }
         if (!lowered) {
-            probe = GroupIR();
-            if ((rc = lower_group(node, fused, &probe, &err_))) return rc;
+            bool done = false;
+            rc = gnode == &node ? try_plain_fill(node, &done) : CN_OK;
+            if (rc) return rc;
+            if (done) {
+                ++*index;
+                return CN_OK;
+            }
+            fused = scan_reductions(after, &j);
+            if (!fused.empty()) {
+                std::string perr;
+                int lrc = lower_group(*gnode, fused, &probe, &perr);
+                bool related = false;
+                if (lrc == CN_OK && probe.cls == GroupIR::SHIFTED) {
+                    // only worth fusing when a reduction operand is produced or read by the group
+                    for (auto& rd : probe.reds)
+                        for (const ValRef* v : {&rd.a, &rd.b}) {
+                            if (v->kind == ValRef::OUTVAL || v->kind == ValRef::ROOT) related = true;
+                            if (v->kind == ValRef::LEAF)
+                                for (auto& l : probe.leaves)
+                                    if (&l != &probe.leaves[v->idx] && l.name == probe.leaves[v->idx].name)
+                                        related = true;
+                        }
+                }
+                if (lrc != CN_OK || probe.cls != GroupIR::SHIFTED || !related) {
+                    fused.clear();
+                    j = after;
+                } else {
+                    lowered = true;  // the probe is the group as it will run
+                }
+            }
+            if (!lowered) {
+                probe = GroupIR();
+                if ((rc = lower_group(*gnode, fused, &probe, &err_))) return rc;
+            }
         }
         CompiledGroup* k = nullptr;
         if ((rc = get_kernel(probe, &k))) return rc;

@@ -94,6 +94,7 @@ struct Stats {
     long long peer_exchanges = 0;    // reductions finished / halos moved through the peer mailboxes
     long long overlapped_sweeps = 0; // stencil sweeps whose interior ran beside the halo exchange
     long long deep_halo_sweeps = 0;  // stencil sweeps that also updated halo rows (no exchange needed next)
+    long long inlined_producers = 0; // whole-array assignments folded into the stencil kernel that reads them
 };
 
 struct DriverApi {
@@ -166,7 +167,9 @@ public:
         plans_.clear();
     }
     void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; plans_.clear(); }
-    void set_flat_prefetch(bool on) { flat_prefetch_ = on; plans_.clear(); }
+    void set_flat_prefetch(int mode) { flat_prefetch_ = mode; plans_.clear(); }
+    void set_fuse_producers(int mode) { fuse_producers_ = mode; plans_.clear(); }
+    void set_stencil_shfl(bool on) { stencil_shfl_ = on; plans_.clear(); }
     void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
     void set_overlap_halo(bool on) { overlap_halo_ = on; }
     void set_deep_halo(bool on) { deep_halo_ = on; }
@@ -222,10 +225,13 @@ private:
     int halo_ = 1;
     bool fuse_reductions_ = true;
     bool debug_drop_copies_ = false;  // test hook: staged kernels issue no tile copies
-    bool flat_prefetch_ = false;      // flat kernels load the next tile ahead of the arithmetic
+    int flat_prefetch_ = -1;          // flat kernels' load placement (TileConfig::prefetch); -1: chosen per group
     int staged_ns_ = 0;               // ring depth of staged 3-D kernels (0: default)
     bool staged_tile_set_ = false;    // the staged tile shape was chosen by the caller
     bool tile_set_ = false;           // the tile shape of the other kernels was chosen by the caller
+    int fuse_producers_ = 2;          // a whole-array assignment + the stencil that reads it as one kernel:
+                                      // 0 never, 1 recomputed per stencil point, 2 staged in shared memory where it fits
+    bool stencil_shfl_ = false;       // cache-served stencil kernels take x-neighbours by warp shuffle
     bool plan_cache_ = true;
     std::unordered_map<uint64_t, Plan> plans_;  // keyed by a hash of the blob bytes
     Plan* recording_ = nullptr;                 // plan being recorded by the running receive_dag

@@ -25,6 +25,7 @@ void array_strides(const Array& a, int64_t* s) {
 
 int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     TileConfig tile = tile_;
+    bool heavy_flat = false;
     if (g.flat && !tile_set_) {
         // exp, tanh, sqrt and division are long dependent chains in double precision: four
         // rows per thread give the scheduler eight independent elements to interleave
@@ -32,6 +33,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         for (auto& r : g.roots)
             if (r.opcode == OP_EXP || r.opcode == OP_TANH || r.opcode == OP_SQRT || r.opcode == OP_DIV) ++heavy;
         if (heavy >= 2) tile.r = 4;
+        heavy_flat = heavy >= 2;
     }
     if (g.staged) {
         // a staged tile is one TMA box: at most 256 elements per side
@@ -39,6 +41,8 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         // measured best: 3-D march 128 columns x 8 rows per plane tile with a 4-deep ring
         // (42 KB of shared memory per block, four blocks per SM); 2-D tiles 128 x 16
         if (g.ndims == 3 && !staged_tile_set_) tile.r = 2;
+        // computed tiles carry a halo ring of redundant work: 128 x 32 points keep it below 10 %
+        if (!g.producer.empty() && !staged_tile_set_) tile.r = 8;
         if (tile.tx > 64) tile.tx = 64;
         while ((CN_BLOCK / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
     }
@@ -47,12 +51,22 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         tile.s0 = g.ndims == 2 ? g.array_shape[1] : g.array_shape[1] * g.array_shape[2];
         tile.s1 = g.ndims == 3 ? g.array_shape[2] : 0;
     }
+    if (!g.producer.empty()) {
+        if (const char* e = getenv("CN_PRODUCER_MINB")) tile.minb = std::max(1, std::min(8, atoi(e)));
+        if (const char* e = getenv("CN_PRODUCER_FILL_U")) tile.fill_u = std::max(1, std::min(9, atoi(e)));
+    }
     tile.drop_copies = g.staged && debug_drop_copies_;
-    tile.prefetch = g.flat && flat_prefetch_;
+    tile.shfl = stencil_shfl_ && g.cls == GroupIR::SHIFTED && !g.flat && !g.staged;
+    // heavy flat groups issue the loads of all their rows before the arithmetic: between the
+    // out-of-line slow paths of exp / sqrt / division the compiler leaves each row's loads
+    // next to their use, and the memory system idles while a row is computed (measured on the
+    // 2^28 chain: 1.18 -> 1.0 ms)
+    tile.prefetch = !g.flat ? 0 : (flat_prefetch_ >= 0 ? flat_prefetch_ : (heavy_flat ? 2 : 0));
     if (g.staged && g.ndims == 3) tile.ns = staged_ns_ ? staged_ns_ : (g.hz == 1 ? 4 : 0);
     std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
                       std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
-                      (tile.prefetch ? "|pf" : "");
+                      "|mb" + std::to_string(tile.minb) + "|fu" + std::to_string(tile.fill_u) +
+                      "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "");
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -73,8 +87,10 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         const char* cls = g.cls == GroupIR::SHIFTED ? (g.flat ? "flat" : "shifted")
                           : (g.cls == GroupIR::STRIDED ? "strided" : "scalar");
         char lbl[160];
+        const size_t n_in = g.producer.empty() ? g.input_arrays().size()
+                                               : g.input_arrays().size() - 1 + g.producer[0].input_arrays().size();
         snprintf(lbl, sizeof(lbl), "group%zu[%s %dd vec%d in%zu out%zu red%zu%s]", kernels_.size(), cls,
-                 g.ndims, g.vec, g.input_arrays().size(), g.outs.size(), g.reds.size(),
+                 g.ndims, g.vec, n_in, g.outs.size(), g.reds.size(),
                  g.copy_through ? " copy-through" : "");
         k.label = lbl;
     }
@@ -83,7 +99,8 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         const size_t sw = (size_t)tile.tx * 2 + 4, sh = (size_t)(CN_BLOCK / tile.tx) * tile.r + 2 * g.hy;
         const size_t slot = (sh * sw + 15) / 16 * 16;
         k.smem_bytes = ns * slot * sizeof(double) + ns * sizeof(unsigned long long);
-        k.label += " tma";
+        if (!g.producer.empty()) k.smem_bytes = slot * sizeof(double) + sizeof(unsigned long long);
+        k.label += g.producer.empty() ? " tma" : " staged-producer";
         if ((rc = driver_fail(drv_.FuncSetAttribute(k.func, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
                                                     (int)k.smem_bytes), "cuFuncSetAttribute")))
             return rc;
@@ -321,7 +338,12 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     if ((int)in_names.size() > CN_MAX_IN) return fail(CN_ERR_LIMIT, "too many input arrays in one group");
     Array* ref = nullptr;
     std::vector<Array*> ins;
+    const bool prod = !g.producer.empty();  // the stage array is a stand-in computed in the kernel
     for (size_t i = 0; i < in_names.size(); ++i) {
+        if (prod && in_names[i] == g.stage_array) {
+            ins.push_back(nullptr);
+            continue;
+        }
         Array* x = find(in_names[i]);
         if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "operand array " + std::to_string(in_names[i]) + " does not exist");
         if ((rc = check_leaf(x, nd, g.array_shape, "group operand"))) return rc;
@@ -341,13 +363,36 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         } else {
             if ((rc = create_array(o.name, nd, g.array_shape, g.dtype, false, &x))) return rc;
             // create_array may have re-hashed the table: refresh the input pointers
-            for (size_t i = 0; i < in_names.size(); ++i) ins[i] = find(in_names[i]);
+            for (size_t i = 0; i < in_names.size(); ++i)
+                if (ins[i]) ins[i] = find(in_names[i]);
             for (size_t j = 0; j < outs.size(); ++j) outs[j] = find(g.outs[j].name);
         }
         outs.push_back(x);
         ref = x;
     }
     if (!ref) return fail(CN_ERR_UNSUPPORTED, "group touches no array");
+    // staged producer: its inputs, literal scalars and size-1 operands follow the group's own
+    std::vector<Array*> pins;
+    if (prod) {
+        const GroupIR& gp = g.producer[0];
+        const std::vector<int> pnames = gp.input_arrays();
+        if (in_names.size() + pnames.size() > CN_MAX_IN) return fail(CN_ERR_LIMIT, "too many input arrays in one group");
+        for (size_t kx = 0; kx < pnames.size(); ++kx) {
+            Array* x = find(pnames[kx]);
+            if (!x) return fail(CN_ERR_UNKNOWN_ARRAY, "operand array " + std::to_string(pnames[kx]) + " does not exist");
+            if ((rc = check_leaf(x, nd, g.array_shape, "group operand"))) return rc;
+            if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "operand dtype differs from the group dtype");
+            pins.push_back(x);
+        }
+        for (size_t i = 0; i < gp.scalars.size(); ++i) a.sc[g.scalars.size() + i] = gp.scalars[i];
+        for (size_t i = 0; i < gp.bcast_names.size(); ++i) {
+            Array* sarr = find(gp.bcast_names[i]);
+            if (!sarr) return fail(CN_ERR_UNKNOWN_ARRAY, "size-1 array " + std::to_string(gp.bcast_names[i]) + " does not exist");
+            if (sarr->global_elems() != 1) return fail(CN_ERR_SHAPE_MISMATCH, "broadcast operand is not a size-1 array");
+            if (sarr->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "size-1 operand dtype differs from the group dtype");
+            a.bc[g.bcast_names.size() + i] = sarr->buf.data;
+        }
+    }
 
     // halos: a leaf shifted along dimension 0 reads rows owned by a neighbour.  Every array
     // keeps count of how many of its halo rows still hold the neighbours' current values
@@ -363,15 +408,20 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
                 if (in_names[i] == l.name) reach[i] = std::max(reach[i], r);
         }
         for (size_t i = 0; i < ins.size(); ++i) {
-            if (reach[i] > ins[i]->halo)
-                return fail(CN_ERR_UNSUPPORTED, "array " + std::to_string(in_names[i]) + " was created with a halo of " +
-                                                    std::to_string(ins[i]->halo) + " rows, the stencil reaches " + std::to_string(reach[i]));
-            if (reach[i] > 0 && ins[i]->halo_fresh < reach[i]) stale.push_back(ins[i]);
+            // what the stencil reads of the stand-in, the producer reads of each of its inputs
+            std::vector<Array*> readers = ins[i] ? std::vector<Array*>{ins[i]} : pins;
+            for (Array* x : readers) {
+                if (reach[i] > x->halo)
+                    return fail(CN_ERR_UNSUPPORTED, "array " + std::to_string(x->name) + " was created with a halo of " +
+                                                        std::to_string(x->halo) + " rows, the stencil reaches " + std::to_string(reach[i]));
+                if (reach[i] > 0 && x->halo_fresh < reach[i] && std::find(stale.begin(), stale.end(), x) == stale.end())
+                    stale.push_back(x);
+            }
         }
         // With a halo deeper than the stencil's reach a sweep can also update rows of the halo
         // itself (the neighbour computes the same values for its own rows), so that the next
         // sweeps need no exchange: one exchange of `halo` rows serves up to halo / reach sweeps.
-        if (deep_halo_ && halo_ > 1 && g.reds.empty() && g.souts.empty() && !g.flat && ref->row_end > ref->row_begin) {
+        if (deep_halo_ && halo_ > 1 && g.reds.empty() && g.souts.empty() && !g.flat && !prod && ref->row_end > ref->row_begin) {
             int64_t e = halo_;
             for (size_t i = 0; i < ins.size(); ++i) {
                 const bool refreshed = std::find(stale.begin(), stale.end(), ins[i]) != stale.end();
@@ -385,12 +435,13 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     // Without a fused reduction the sweep can be cut along dimension 0: the rows next to the
     // slab edges wait for the neighbours' halo rows on a second stream while the interior,
     // which needs none of them, runs on the main stream.
-    const bool overlap = overlap_halo_ && !stale.empty() && g.reds.empty() && g.souts.empty() && !g.flat && ext == 0;
+    const bool overlap = overlap_halo_ && !stale.empty() && g.reds.empty() && g.souts.empty() && !g.flat && !prod && ext == 0;
     if (!overlap)
         for (Array* x : stale)
             if ((rc = exchange_halo(x, stream_))) return rc;
 
-    for (size_t i = 0; i < ins.size(); ++i) a.in[i] = ins[i]->buf.data;
+    for (size_t i = 0; i < ins.size(); ++i) a.in[i] = ins[i] ? ins[i]->buf.data : nullptr;
+    for (size_t kx = 0; kx < pins.size(); ++kx) a.in[ins.size() + kx] = pins[kx]->buf.data;
     for (size_t m = 0; m < outs.size(); ++m) {
         Array* x = outs[m];
         a.old[m] = x->buf.data;
@@ -494,7 +545,19 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         }
     }
         if (ntiles >= (1LL << 31)) return fail(CN_ERR_LIMIT, "too many tiles for one launch");
-    if (g.staged) {
+    if (g.staged && prod) {
+        // rows and columns of the producer's inputs that hold data: the slab plus the halo
+        // rows towards every neighbour that exists
+        int64_t h = 0;
+        if (nranks_ > 1 && !ref->replicated) {
+            h = ref->halo;
+            for (Array* x : pins) h = std::min<int64_t>(h, x->halo);
+        }
+        a.fill_lo[0] = rb > 0 ? -h : 0;
+        a.fill_hi[0] = (re - rb) + (re < ref->shape[0] ? h : 0);
+        a.fill_lo[1] = 0;
+        a.fill_hi[1] = ref->shape[nd - 1];
+    } else if (g.staged) {
         Array* sx = find(g.stage_array);
         if (!sx) return fail(CN_ERR_UNKNOWN_ARRAY, "stencil array vanished");
         if ((rc = encode_tensor_map(*sx, *k, g, &a))) return rc;
@@ -540,7 +603,8 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         if (g.flat) vol = (double)ref->local_elems();
         else for (int d = 0; d < nd; ++d) vol *= (double)std::max<int64_t>(0, hi[d] - lo[d]);
         if (empty) vol = 0;
-        double bytes = vol * (double)(in_names.size() + g.outs.size()) * dtype_size(g.dtype);
+        const size_t n_arrays = in_names.size() + g.outs.size() + (prod ? pins.size() - 1 : 0);
+        double bytes = vol * (double)n_arrays * dtype_size(g.dtype);
         bool done = false;
         if (overlap && !empty) {
             // rows [0, H) and [nl - H, nl) of the slab read halo rows; everything between does not

@@ -85,6 +85,13 @@ struct GroupIR {
     int stage_array = -1;       // name of that array
     int hy = 0, hz = 0;         // halo rows / planes a tile carries on each side
 
+    // Staged producer: the stage array is a stand-in that exists nowhere; the kernel computes
+    // its tiles (halo included) in shared memory by evaluating this flat group, whose single
+    // output is the array the stand-in takes the place of (`producer_target`), at every point
+    // of the tile.  Empty, or exactly one element.
+    std::vector<GroupIR> producer;
+    int producer_target = -1;
+
     std::vector<LeafIR> leaves;
     std::vector<double> scalars;
     std::vector<int> bcast_names;
@@ -109,6 +116,20 @@ struct GroupIR {
 // whose caller supplies explicit strided views).
 int lower_group(const DagNode& node, const std::vector<const AstNode*>& fused, GroupIR* out,
                 std::string* err, bool force_strided = false);
+
+// Producer inlining (fuse.cpp): when node `a` assigns a whole array from an elementwise
+// expression of whole arrays and node `b`, right behind it, reads that array through shifted
+// views, build in `out` one node that does the work of both without the round trip of the
+// array through memory.  False when the pair does not fit.
+bool inline_producer(const DagNode& a, const DagNode& b, DagNode* out);
+
+// The staged form of the same pair: `consumer` / `producer` / the stand-in's name as built by
+// stage_producer; lower_staged_producer lowers both and joins them into one GroupIR (2-D
+// float64 groups only; CN_ERR_UNSUPPORTED when the pair does not fit the staged kernel).
+bool stage_producer(const DagNode& a, const DagNode& b, DagNode* consumer, DagNode* producer, int* pseudo_name,
+                    int* target_name);
+int lower_staged_producer(const DagNode& consumer, const DagNode& producer, int pseudo_name, int target_name,
+                          const std::vector<const AstNode*>& fused, GroupIR* out, std::string* err);
 
 // Shared-memory / TMA staging of stencil groups.  Level 0: never; 1 (default): 3-D groups
 // only; 2: 2-D groups too.  Set with CN_STAGED or cn_set_option(ctx, "staged", level).

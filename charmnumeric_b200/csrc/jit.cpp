@@ -86,13 +86,17 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
     std::string d_s0 = "-DCN_S0=" + std::to_string(tile.s0) + "LL";
     std::string d_s1 = "-DCN_S1=" + std::to_string(tile.s1) + "LL";
     std::string d_ns = "-DCN_NS_OVERRIDE=" + std::to_string(tile.ns);
+    std::string d_mb = "-DCN_MINB=" + std::to_string(tile.minb > 0 ? tile.minb : 1);
+    std::string d_fu = "-DCN_FILL_U=" + std::to_string(tile.fill_u > 0 ? tile.fill_u : 1);
+    std::string d_pf = "-DCN_PREFETCH=" + std::to_string(tile.prefetch);
     // --fmad=false: a*b+c stays two roundings, as in the reference's arith.mulf/addf pairs
     // (src/jit.cpp:411-443); division and sqrt stay IEEE-rounded (the defaults, spelled out).
     const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false",    "--prec-div=true",
                           "--prec-sqrt=true",           "--std=c++17",     "-lineinfo",
                           d_tx.c_str(),                 d_r.c_str(),       d_s0.c_str(),
                           d_s1.c_str(),                 d_ns.c_str(),
-                          tile.prefetch ? "-DCN_PREFETCH=1" : "-DCN_PREFETCH=0",
+                          d_mb.c_str(),                 d_fu.c_str(),
+                          d_pf.c_str(),                 tile.shfl ? "-DCN_SHFL=1" : "-DCN_SHFL=0",
                           tile.drop_copies ? "-DCN_DEBUG_DROP_COPIES=1" : "-DCN_DEBUG_DROP_COPIES=0",
                           tile.drop_copies ? "-DCN_WAIT_LIMIT=2000u" : "-DCN_WAIT_LIMIT=2000000u"};
     rc = api->CompileProgram(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);

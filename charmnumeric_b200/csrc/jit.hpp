@@ -22,8 +22,15 @@ struct TileConfig {
     // test hook of the staged kernels: issue no tile copies and give up waiting quickly
     bool drop_copies = false;
     int ns = 0;  // ring depth of the staged kernels (0: the generator's default)
-    // flat kernels: request the next tile's inputs before this tile's arithmetic starts
-    bool prefetch = false;
+    // flat kernels: 0 loads where they are used; 1 the next tile's inputs are requested before
+    // this tile's arithmetic starts (register double buffering); 2 all loads of a tile are
+    // issued up front, ahead of its arithmetic
+    int prefetch = 0;
+    // stencil kernels: single neighbours along the last dimension come from the neighbour
+    // lanes' registers (warp shuffle) instead of their own loads
+    bool shfl = false;
+    int minb = 1;    // resident blocks per SM the compiler has to leave room for (register cap)
+    int fill_u = 3;  // staged producers: points per thread whose loads are issued together
 };
 
 // Compile CUDA source to a cubin image for sm_100a.  Works without a GPU.

@@ -72,6 +72,7 @@ struct Lowering {
     std::map<int, int> bc_by_name;
     bool force_strided = false;
     bool allow_staged = true;
+    bool force_staged = false;  // stage whatever the process-wide level says (staged producers)
 
     int fail(int code, const std::string& m) {
         if (err) *err = m;
@@ -577,11 +578,13 @@ struct Lowering {
             else return false;
         }
         if (copy_through) {
-            // the sweep must cover the whole array and hazard outputs must be region outputs
+            // the sweep must cover the whole array; a hazard output is either a region output
+            // (the rest of the array is copied through) or an assignment of the whole array
+            // (every element is written anyway: nothing to copy through)
             for (int d = 0; d < nd; ++d)
                 if (boxes[big].lo[d] != 0 || boxes[big].hi[d] != as[d]) return false;
             for (size_t i = 0; i < g.outs.size(); ++i)
-                if (g.outs[i].hazard && out_box[i] != small) return false;
+                if (g.outs[i].hazard && out_box[i] != small && out_box[i] != big) return false;
         }
 
         // commit
@@ -659,7 +662,7 @@ struct Lowering {
         // old contents: copy-through of hazard outputs, or forwarding outside the region
         for (size_t i = 0; i < g.outs.size(); ++i) {
             OutIR& o = g.outs[i];
-            if (o.hazard && g.two_domains) o.needs_old = true;
+            if (o.hazard && g.two_domains && o.domain == DOM_REGION) o.needs_old = true;
         }
         auto mark_old = [&](const ValRef& v) {
             if (v.kind == ValRef::OUTVAL && g.outs[v.idx].domain == DOM_REGION)
@@ -684,7 +687,7 @@ struct Lowering {
         // staged variant: exactly one array is read at shifted positions, within a small halo
         g.staged = false;
         const int level = staged_level();
-        if (allow_staged && (level == 2 || (level == 1 && nd == 3)) && !g.flat && g.vec == 2 &&
+        if (allow_staged && (force_staged || level == 2 || (level == 1 && nd == 3)) && !g.flat && g.vec == 2 &&
             g.dtype == DT_F64 && (nd == 2 || nd == 3)) {
             int name = -1;
             bool ok = true;
@@ -838,6 +841,65 @@ int lower_group(const DagNode& node, const std::vector<const AstNode*>& fused, G
     return CN_OK;
 }
 
+int lower_staged_producer(const DagNode& consumer, const DagNode& producer, int pseudo_name, int target_name,
+                          const std::vector<const AstNode*>& fused, GroupIR* out, std::string* err) {
+    auto unfit = [&](const char* why) {
+        if (err) *err = why;
+        return (int)CN_ERR_UNSUPPORTED;
+    };
+    GroupIR gp;
+    {
+        Lowering lp{producer, gp, err, {}, {}, {}, {}, false, false};
+        int rc = lp.run({});
+        if (rc) return rc;
+    }
+    if (gp.cls != GroupIR::SHIFTED || !gp.flat || gp.outs.size() != 1 || !gp.outs[0].is_set ||
+        gp.outs[0].name != target_name || !gp.reds.empty() || !gp.souts.empty() || gp.dtype != DT_F64)
+        return unfit("producer is not a flat float64 group with one output");
+    if (gp.outs[0].value.kind != ValRef::ROOT) return unfit("producer output is not a computed value");
+    {
+        Lowering lc{consumer, *out, err, {}, {}, {}, {}, false, true};
+        lc.force_staged = true;
+        int rc = lc.run(fused);
+        if (rc) return rc;
+    }
+    GroupIR& g = *out;
+    if (g.cls != GroupIR::SHIFTED || g.flat || !g.staged || g.stage_array != pseudo_name || g.ndims != 2 ||
+        g.dtype != DT_F64 || g.vec != 2)
+    {
+        if (err)
+            *err = "consumer does not lower to a staged 2-D float64 stencil over the stand-in (class " +
+                   std::to_string((int)g.cls) + ", flat " + std::to_string(g.flat) + ", staged " + std::to_string(g.staged) +
+                   ", stage array " + std::to_string(g.stage_array) + ", rank " + std::to_string(g.ndims) + ", vec " +
+                   std::to_string(g.vec) + ")";
+        return (int)CN_ERR_UNSUPPORTED;
+    }
+    if (gp.ndims != g.ndims) return unfit("producer and consumer ranks differ");
+    for (int d = 0; d < g.ndims; ++d)
+        if (gp.array_shape[d] != g.array_shape[d]) return unfit("producer and consumer shapes differ");
+    for (int d = 0; d < g.ndims; ++d)
+        if (g.box_lo[d] != 0 || g.box_hi[d] != g.array_shape[d]) return unfit("consumer does not sweep the whole array");
+    if (g.scalars.size() + gp.scalars.size() > CN_MAX_SC || g.bcast_names.size() + gp.bcast_names.size() > CN_MAX_BC ||
+        g.input_arrays().size() + gp.input_arrays().size() > CN_MAX_IN)
+        return unfit("too many operands for one launch");
+    // Other blocks evaluate the producer on their tiles' halo rings while this block stores:
+    // an output that the producer reads must go to the shadow buffer.
+    const std::vector<int> pin = gp.input_arrays();
+    for (auto& o : g.outs)
+        if (std::find(pin.begin(), pin.end(), o.name) != pin.end()) {
+            const bool whole = region_is_full(o.region, o.ndims, o.shape);
+            if (!whole && o.domain != DOM_REGION) return unfit("an output the producer reads is neither whole nor the region");
+            o.hazard = true;
+            g.copy_through = true;
+            if (g.two_domains && o.domain == DOM_REGION) o.needs_old = true;
+        }
+    g.producer.clear();
+    g.producer.push_back(gp);
+    g.producer_target = target_name;
+    if ((int)g.leaves.size() > 32) return unfit("too many array operands in one group");
+    return CN_OK;
+}
+
 std::vector<int> GroupIR::input_arrays() const {
     std::vector<int> names;
     for (auto& l : leaves) {
@@ -910,6 +972,7 @@ std::string GroupIR::key() const {
         put(s, r.b);
         s << ';';
     }
+    if (!producer.empty()) s << "|P{" << producer[0].key() << "}";
     return s.str();
 }
 

@@ -140,6 +140,12 @@ int cn_dag_check(const char* msg, int64_t size, int* n_nodes, int* n_roots, char
 int cn_group_compile_check(const char* node_blob, int64_t size, char* source, int64_t cap,
                            int64_t* cubin_bytes, char* err, int errcap);
 
+/* Host-only: would node_a (a whole-array elementwise assignment) and node_b (a stencil group
+ * over the assigned array) run as one kernel?  *fused = 1 and the kernel's CUDA source when the
+ * pair fits the pattern, lowers and compiles for sm_100a; *fused = 0 otherwise. */
+int cn_fuse_check(const char* node_a, int64_t size_a, const char* node_b, int64_t size_b,
+                  char* source, int64_t cap, int* fused, char* err, int errcap);
+
 /* Rows [*begin, *end) of dimension 0 that `rank` of `nranks` owns for an array with n0 rows
  * (host-only).  Takes the place of the reference's tile -> chare map
  * (ArrayDecomp::owning_chare / chare_region_global, src/array_region.hpp:357-368): here one
@@ -192,6 +198,7 @@ typedef struct cn_stats {
     int64_t peer_exchanges;    /* reductions finished in-kernel / halos moved through peer mailboxes */
     int64_t overlapped_sweeps; /* stencil sweeps whose interior ran beside the halo exchange */
     int64_t deep_halo_sweeps;  /* stencil sweeps that also updated halo rows (see option "halo") */
+    int64_t inlined_producers; /* whole-array assignments folded into the stencil kernel behind them */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
@@ -203,14 +210,22 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
  * the last dimension, rows per thread), "staged" 0/1/2 (TMA / shared-memory staging of stencil
  * tiles: never / 3-D groups only (default) / 2-D groups too; process-wide), "staged_tile_tx" /
  * "staged_tile_rows", "profile" 0/1, "plan_cache" 0/1 (default 1: a DAG blob whose bytes,
- * epoch aside, have run before skips parsing and lowering), "flat_prefetch" 0/1 (default 0:
- * flat kernels request the next tile's inputs before the arithmetic of the current one),
+ * epoch aside, have run before skips parsing and lowering), "flat_prefetch" -1/0/1/2 (where flat
+ * kernels place their loads: 0 next to their use, 1 the next tile's inputs are requested before
+ * the arithmetic of the current one, 2 all loads of a tile ahead of its arithmetic; default -1:
+ * 2 for groups heavy in exp / tanh / sqrt / division, 0 otherwise),
  * "p2p" 0/1 (default 1; read by cn_comm_init: map every rank's mailbox into every other rank
  * with CUDA IPC, finish reductions inside the producing kernel and move halo rows as NVLink
  * peer stores; when the mapping cannot be set up on all ranks, NCCL does both),
  * "overlap_halo" 0/1 (default 0: a stencil sweep without a fused reduction is cut along
  * dimension 0; the halo exchange and the rows next to the slab edges run on a second stream
- * beside the interior). */
+ * beside the interior), "fuse_producers" 0/1/2 (a whole-array elementwise assignment
+ * directly followed by a stencil group over the assigned array runs as one kernel instead of
+ * writing the array and reading it back: 1 the assigned values are recomputed at every stencil
+ * point, 2 (default) they are computed tile by tile, halo ring included, into shared memory
+ * where that form fits (2-D float64), recomputed otherwise; 0 two kernels),
+ * "stencil_shfl" 0/1 (default 0, measured slower: cache-served stencil kernels take the
+ * neighbours along the last dimension from neighbour lanes by warp shuffle). */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);
 
 #ifdef __cplusplus

@@ -448,3 +448,89 @@ def test_rank_marked_failed_stops_collective_work():
         assert e.value.status == 14
     finally:
         ctx.close()
+
+
+# ---- producer inlining: a whole-array assignment folded into the stencil behind it -----------
+
+def _cg_rotated_program(m0, m1, iters):
+    """CG entered at the direction update, the order the benchmark's step uses."""
+    def prog():
+        b = cnp.zeros((m0, m1))
+        b[1:-1, 1:-1] = cnp.random.uniform((m0, m1), seed=0x5EED + 3)[1:-1, 1:-1]
+        x = cnp.zeros((m0, m1))
+        r = b.copy()
+        p = b.copy()
+        Ap = cnp.zeros((m0, m1))
+        rtr = cnp.dot2d(r, r)
+        beta = cnp.zeros((1,))
+        out = {}
+        for k in range(iters):
+            p[...] = r + beta * p
+            Ap[1:-1, 1:-1] = (4.0 * p[1:-1, 1:-1] - p[:-2, 1:-1] - p[2:, 1:-1]
+                              - p[1:-1, :-2] - p[1:-1, 2:])
+            pAp = cnp.dot2d(p, Ap)
+            alpha = rtr / pAp
+            x[...] = x + alpha * p
+            r[...] = r - alpha * Ap
+            rtr_new = cnp.dot2d(r, r)
+            beta[...] = rtr_new / rtr
+            rtr[...] = rtr_new
+            out[f"rtr{k}"] = rtr_new
+        out.update({"x": x, "r": r, "p": p, "Ap": Ap})
+        return out
+    return prog
+
+
+@pytest.mark.parametrize("shape,iters", [((10, 10), 4), ((66, 130), 12), ((258, 258), 25)])
+def test_cg_direction_update_inlined_into_stencil(interface, shape, iters):
+    before = interface.context.stats()
+    gpu, cpu = run_both(interface, _cg_rotated_program(shape[0], shape[1], iters))
+    after = interface.context.stats()
+    assert_rel(gpu, cpu, RTOL_REDUCTION)
+    assert after["inlined_producers"] - before["inlined_producers"] == iters
+    # one iteration = (p, Ap, p.Ap) + (x, r, r.r) + one size-1 kernel
+    assert after["fused_reductions"] - before["fused_reductions"] >= 2 * iters
+
+
+def test_inlined_producer_is_bit_exact(interface):
+    """One direction update + stencil from seeded data: p and Ap must carry the very bits the
+    two separate kernels (and the oracle) produce, on every shape class of tile."""
+    for shape in [(7, 9), (64, 64), (131, 258), (40, 20, 34)]:
+        def prog():
+            nd = len(shape)
+            r = cnp.random.uniform(shape, seed=71, low=-1.0, high=1.0)
+            p = cnp.random.uniform(shape, seed=72, low=-1.0, high=1.0)
+            beta = cnp.random.uniform((1,), seed=73)
+            Ap = cnp.zeros(shape)
+            p[...] = r + beta * p
+            if nd == 2:
+                Ap[1:-1, 1:-1] = (4.0 * p[1:-1, 1:-1] - p[:-2, 1:-1] - p[2:, 1:-1]
+                                  - p[1:-1, :-2] - p[1:-1, 2:])
+            else:
+                Ap[1:-1, 1:-1, 1:-1] = (6.0 * p[1:-1, 1:-1, 1:-1] - p[:-2, 1:-1, 1:-1] - p[2:, 1:-1, 1:-1]
+                                        - p[1:-1, :-2, 1:-1] - p[1:-1, 2:, 1:-1]
+                                        - p[1:-1, 1:-1, :-2] - p[1:-1, 1:-1, 2:])
+            return {"p": p, "Ap": Ap, "pAp": cnp.dot2d(p, Ap)}
+        before = interface.context.stats()
+        gpu, cpu = run_both(interface, prog)
+        after = interface.context.stats()
+        assert after["inlined_producers"] - before["inlined_producers"] == 1, shape
+        assert_bit_exact({k: gpu[k] for k in ("p", "Ap")}, {k: cpu[k] for k in ("p", "Ap")})
+        assert_rel({"pAp": gpu["pAp"]}, {"pAp": cpu["pAp"]}, RTOL_REDUCTION)
+
+
+def test_producer_not_inlined_when_the_stencil_overwrites_its_input(interface):
+    """`p = r + beta p` followed by a stencil that assigns into r: the pair must stay two
+    kernels (the stencil's writes would feed back into the recomputed p), and stay correct."""
+    def prog():
+        r = cnp.random.uniform((33, 40), seed=81)
+        p = cnp.random.uniform((33, 40), seed=82)
+        beta = cnp.random.uniform((1,), seed=83)
+        p[...] = r + beta * p
+        r[1:-1, 1:-1] = 0.25 * (p[:-2, 1:-1] + p[2:, 1:-1] + p[1:-1, :-2] + p[1:-1, 2:])
+        return {"p": p, "r": r}
+    before = interface.context.stats()
+    gpu, cpu = run_both(interface, prog)
+    after = interface.context.stats()
+    assert after["inlined_producers"] == before["inlined_producers"]
+    assert_bit_exact(gpu, cpu)

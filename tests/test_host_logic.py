@@ -271,3 +271,50 @@ def test_exp_tables_of_oracle_and_device_are_identical():
     consts_orc = [float.fromhex(re.search(name + r"\s*=\s*(" + hexf + ")", orc).group(1))
                   for name in ("CNO_C_HI", "CNO_C_LO", "CNO_INV")]
     assert [v.hex() for v in consts_dev] == [v.hex() for v in consts_orc]
+
+
+def _pending_nodes():
+    return [n for kind, n in F.build_nodes(F._state.pending) if kind == "node"]
+
+
+def test_direction_update_and_stencil_compile_as_one_kernel():
+    """Host side of the producer inlining: `p = r + beta p` and the 5-point stencil over p
+    become one kernel that reads r and p and writes p and Ap."""
+    from charmnumeric_b200.context import fuse_check
+    cnp.reset_frontend_state()
+    m = 66
+    p, r, Ap, beta = cnp.zeros((m, m)), cnp.zeros((m, m)), cnp.zeros((m, m)), cnp.zeros((1,))
+    F._state.pending = []
+    p[...] = r + beta * p
+    Ap[1:-1, 1:-1] = 4.0 * p[1:-1, 1:-1] - p[:-2, 1:-1] - p[2:, 1:-1] - p[1:-1, :-2] - p[1:-1, 2:]
+    nodes = _pending_nodes()
+    assert len(nodes) == 2
+    src = fuse_check(nodes[0], nodes[1])
+    # the staged form: the stencil reads a stand-in whose tiles the kernel computes from r and p
+    assert src is not None and "cn_group_shifted2d_i1o2" in src and "Pin1" in src and "ring" in src
+    import os
+    os.environ["CN_FUSE_PRODUCERS"] = "1"
+    try:
+        cloned = fuse_check(nodes[0], nodes[1])  # the form that recomputes at every stencil point
+    finally:
+        del os.environ["CN_FUSE_PRODUCERS"]
+    assert cloned is not None and "cn_group_shifted2d_i2o2" in cloned
+    # a stencil that assigns into the producer's own input must not fuse
+    cnp.reset_frontend_state()
+    F._state.pending = []
+    p2, r2, beta2 = cnp.zeros((m, m)), cnp.zeros((m, m)), cnp.zeros((1,))
+    F._state.pending = []
+    p2[...] = r2 + beta2 * p2
+    r2[1:-1, 1:-1] = 0.25 * (p2[:-2, 1:-1] + p2[2:, 1:-1] + p2[1:-1, :-2] + p2[1:-1, 2:])
+    nodes = _pending_nodes()
+    assert len(nodes) == 2 and fuse_check(nodes[0], nodes[1]) is None
+    # and neither does a pair whose first node is not a whole-array assignment
+    cnp.reset_frontend_state()
+    F._state.pending = []
+    p3, r3 = cnp.zeros((m, m)), cnp.zeros((m, m))
+    F._state.pending = []
+    p3[1:-1, :] = r3[1:-1, :] + 1.0
+    r3[1:-1, 1:-1] = p3[:-2, 1:-1] + p3[2:, 1:-1]
+    nodes = _pending_nodes()
+    assert fuse_check(nodes[0], nodes[-1]) is None
+    cnp.reset_frontend_state()
