@@ -418,8 +418,11 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
     int rc;
     if (peer_.ready) {
         if ((size_t)cnt * esz <= CN_PEER_HALO_SLOT && (cnt * esz) % 8 == 0) {
-            if (has_prev || has_next)
-                if ((rc = exchange_halo_p2p(a, has_prev, has_next, st))) return rc;
+            if (has_prev || has_next) {
+                const std::vector<Array*> one{a};
+                rc = exchange_halo_p2p(one, has_prev, has_next, st);
+                if (rc) return rc;
+            }
             a->halo_fresh = a->halo;
             stats_.halo_exchanges++;
             return CN_OK;
@@ -443,27 +446,79 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
     return CN_OK;
 }
 
+// The halo rows of several arrays at once.  Arrays of one row partition whose rows fit the
+// payload slot together travel in ONE peer-store launch (CG's fused kernel needs r and p: one
+// exchange latency instead of two); anything else goes array by array.
+int Context::exchange_halos(const std::vector<Array*>& arrays, cudaStream_t st) {
+    std::vector<Array*> todo;
+    for (Array* a : arrays)
+        if (!(nranks_ == 1 || a->replicated || (a->halo > 0 && a->halo_fresh == a->halo))) todo.push_back(a);
+    bool batch = peer_.ready && todo.size() > 1 && todo.size() <= CN_HALO_PARTS && comm_.ready;
+    size_t total = 0;
+    for (Array* a : todo) {
+        const size_t bytes = (size_t)a->halo * a->unit * dtype_size(a->dtype);
+        if (a->shape[0] != todo[0]->shape[0] || a->halo != todo[0]->halo || bytes % 8 || a->local_rows() < a->halo) batch = false;
+        total += (bytes + 15) & ~(size_t)15;
+    }
+    if (batch && total <= CN_PEER_HALO_SLOT) {
+        Array* a = todo[0];
+        const int H = a->halo;
+        const int64_t nl = a->local_rows();
+        int64_t b, e;
+        bool has_prev = false, has_next = false, thin = false;
+        if (nl > 0 && rank_ > 0) {
+            partition(a->shape[0], &b, &e, rank_ - 1);
+            has_prev = e > b;
+            thin = thin || (has_prev && e - b < H);
+        }
+        if (nl > 0 && rank_ + 1 < nranks_) {
+            partition(a->shape[0], &b, &e, rank_ + 1);
+            has_next = e > b;
+            thin = thin || (has_next && e - b < H);
+        }
+        if (!thin) {
+            int rc = CN_OK;
+            if (has_prev || has_next)
+                if ((rc = exchange_halo_p2p(todo, has_prev, has_next, st))) return rc;
+            for (Array* x : todo) x->halo_fresh = x->halo;
+            stats_.halo_exchanges++;
+            return CN_OK;
+        }
+    }
+    for (Array* a : todo) {
+        int rc = exchange_halo(a, st);
+        if (rc) return rc;
+    }
+    return CN_OK;
+}
+
 // Halo rows as peer stores: one small kernel pushes this rank's boundary rows into the
 // neighbours' mailboxes, publishes them with a flag, waits (bounded) for the neighbours' rows
 // and copies them into the local halo.
-int Context::exchange_halo_p2p(Array* a, bool has_prev, bool has_next, cudaStream_t st) {
-    const size_t esz = dtype_size(a->dtype);
-    const size_t bytes = (size_t)a->halo * a->unit * esz;
-    const int64_t nl = a->local_rows();
+int Context::exchange_halo_p2p(const std::vector<Array*>& arrays, bool has_prev, bool has_next, cudaStream_t st) {
     HaloArgs h;
-    h.bytes = bytes;
+    h.nparts = (int)arrays.size();
+    double total = 0;
+    for (size_t q = 0; q < arrays.size(); ++q) {
+        Array* a = arrays[q];
+        const size_t esz = dtype_size(a->dtype);
+        const size_t bytes = (size_t)a->halo * a->unit * esz;
+        const int64_t nl = a->local_rows();
+        h.bytes[q] = bytes;
+        h.first_rows[q] = a->buf.data;
+        h.last_rows[q] = a->buf.data + ((size_t)nl * a->unit * esz - bytes);
+        h.halo_below[q] = a->buf.data - bytes;
+        h.halo_above[q] = a->buf.data + (size_t)nl * a->unit * esz;
+        total += (double)bytes;
+    }
     if (has_prev) h.epoch_prev = ++peer_.epoch_prev;
     if (has_next) h.epoch_next = ++peer_.epoch_next;
     h.me = peer_.mine;
     h.box_prev = has_prev ? peer_.box[rank_ - 1] : nullptr;
     h.box_next = has_next ? peer_.box[rank_ + 1] : nullptr;
-    h.first_rows = a->buf.data;
-    h.last_rows = a->buf.data + ((size_t)nl * a->unit * esz - bytes);
-    h.halo_below = a->buf.data - bytes;
-    h.halo_above = a->buf.data + (size_t)nl * a->unit * esz;
     h.ticket = peer_.ticket;
     h.error = error_word_;
-    prof_start("halo exchange (peer stores)", (double)bytes * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)), st);
+    prof_start("halo exchange (peer stores)", total * ((has_prev ? 2 : 0) + (has_next ? 2 : 0)), st);
     int rc = cuda_fail(launch_halo_exchange(h, sm_count_, st), "halo exchange");
     prof_stop();
     if (rc) return rc;
@@ -490,12 +545,12 @@ int Context::debug_peer_wait() {
     cudaMemsetAsync(box, 0, sizeof(CnPeerBox) + 64, stream_);
     cudaMemsetAsync(ticket, 0, 256, stream_);
     HaloArgs h;
-    h.bytes = 64;
+    h.bytes[0] = 64;
     h.epoch_prev = 2;
     h.me = box;
     h.box_prev = box;
-    h.first_rows = (const char*)box + sizeof(CnPeerBox);      // any 64 readable bytes
-    h.halo_below = (char*)box + sizeof(CnPeerBox) + 256;
+    h.first_rows[0] = (const char*)box + sizeof(CnPeerBox);      // any 64 readable bytes
+    h.halo_below[0] = (char*)box + sizeof(CnPeerBox) + 256;
     h.ticket = ticket;
     h.error = error_word_;
     h.wait_limit = 20000;

@@ -212,7 +212,8 @@ private:
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);
     int exchange_halo(Array* a, cudaStream_t st);
-    int exchange_halo_p2p(Array* a, bool has_prev, bool has_next, cudaStream_t st);
+    int exchange_halos(const std::vector<Array*>& arrays, cudaStream_t st);
+    int exchange_halo_p2p(const std::vector<Array*>& arrays, bool has_prev, bool has_next, cudaStream_t st);
     int ensure_second_stream();
     int setup_peer_boxes();
     void bind_peers(CnGroupArgs* a);

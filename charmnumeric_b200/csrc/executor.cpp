@@ -437,8 +437,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     // which needs none of them, runs on the main stream.
     const bool overlap = overlap_halo_ && !stale.empty() && g.reds.empty() && g.souts.empty() && !g.flat && !prod && ext == 0;
     if (!overlap)
-        for (Array* x : stale)
-            if ((rc = exchange_halo(x, stream_))) return rc;
+        if ((rc = exchange_halos(stale, stream_))) return rc;
 
     for (size_t i = 0; i < ins.size(); ++i) a.in[i] = ins[i] ? ins[i]->buf.data : nullptr;
     for (size_t kx = 0; kx < pins.size(); ++kx) a.in[ins.size() + kx] = pins[kx]->buf.data;

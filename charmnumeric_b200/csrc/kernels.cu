@@ -410,8 +410,14 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_
     __shared__ int arrived;
     const int bp = (int)(h.epoch_prev & 1ULL), bn = (int)(h.epoch_next & 1ULL);
     // rows for the rank below arrive there "from above" (dir 1), and the other way round
-    if (h.box_prev) halo_copy(halo_slot(h.box_prev, bp, 1), h.first_rows, h.bytes, vec_push != 0);
-    if (h.box_next) halo_copy(halo_slot(h.box_next, bn, 0), h.last_rows, h.bytes, vec_push != 0);
+    {
+        size_t off = 0;
+        for (int q = 0; q < h.nparts; ++q) {
+            if (h.box_prev) halo_copy(halo_slot(h.box_prev, bp, 1) + off, h.first_rows[q], h.bytes[q], vec_push != 0);
+            if (h.box_next) halo_copy(halo_slot(h.box_next, bn, 0) + off, h.last_rows[q], h.bytes[q], vec_push != 0);
+            off += (h.bytes[q] + 15) & ~(size_t)15;
+        }
+    }
     __syncthreads();
     // One thread per block orders the block's stores (the barrier makes them its predecessors)
     // before its ticket; the release stores of the last ticket holder then publish everything.
@@ -436,18 +442,30 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_
     }
     __syncthreads();
     if (!arrived) return;
-    if (h.box_prev) halo_unpack(h.halo_below, halo_slot(h.me, bp, 0), h.bytes, vec_pull != 0);
-    if (h.box_next) halo_unpack(h.halo_above, halo_slot(h.me, bn, 1), h.bytes, vec_pull != 0);
+    size_t off = 0;
+    for (int q = 0; q < h.nparts; ++q) {
+        if (h.box_prev) halo_unpack(h.halo_below[q], halo_slot(h.me, bp, 0) + off, h.bytes[q], vec_pull != 0);
+        if (h.box_next) halo_unpack(h.halo_above[q], halo_slot(h.me, bn, 1) + off, h.bytes[q], vec_pull != 0);
+        off += (h.bytes[q] + 15) & ~(size_t)15;
+    }
 }
 
 }  // namespace
 
 cudaError_t launch_halo_exchange(const HaloArgs& h, int sm_count, cudaStream_t s) {
-    if (h.bytes == 0 || (!h.box_prev && !h.box_next)) return cudaSuccess;
-    if (h.bytes % 8 || h.bytes > CN_PEER_HALO_SLOT) return cudaErrorInvalidValue;
-    const bool vec_push = h.bytes % 16 == 0 && (((uintptr_t)h.first_rows | (uintptr_t)h.last_rows) & 15) == 0;
-    const bool vec_pull = h.bytes % 16 == 0 && (((uintptr_t)h.halo_below | (uintptr_t)h.halo_above) & 15) == 0;
-    long long blocks = (long long)((h.bytes + 256 * 64 - 1) / (256 * 64));  // 64 bytes per thread
+    if (h.nparts < 1 || h.nparts > CN_HALO_PARTS) return cudaErrorInvalidValue;
+    size_t total = 0, largest = 0;
+    bool vec_push = true, vec_pull = true;
+    for (int q = 0; q < h.nparts; ++q) {
+        if (h.bytes[q] % 8) return cudaErrorInvalidValue;
+        total += (h.bytes[q] + 15) & ~(size_t)15;
+        largest = std::max(largest, h.bytes[q]);
+        vec_push = vec_push && h.bytes[q] % 16 == 0 && (((uintptr_t)h.first_rows[q] | (uintptr_t)h.last_rows[q]) & 15) == 0;
+        vec_pull = vec_pull && h.bytes[q] % 16 == 0 && (((uintptr_t)h.halo_below[q] | (uintptr_t)h.halo_above[q]) & 15) == 0;
+    }
+    if (largest == 0 || (!h.box_prev && !h.box_next)) return cudaSuccess;
+    if (total > CN_PEER_HALO_SLOT) return cudaErrorInvalidValue;
+    long long blocks = (long long)((largest + 256 * 64 - 1) / (256 * 64));  // 64 bytes per thread
     int grid = (int)std::max<long long>(1, std::min<long long>(blocks, sm_count > 0 ? sm_count : 148));
     halo_exchange_kernel<<<grid, 256, 0, s>>>(h, vec_push ? 1 : 0, vec_pull ? 1 : 0);
     return cudaGetLastError();

@@ -40,15 +40,19 @@ cudaError_t launch_tile(void* dst, const int64_t dst_shape[3], int64_t dst_row_b
 // Halo exchange through the peer mailboxes (takes the place of the per-edge messages of
 // src/executor_core.cpp:7-143 and PartitionImpl::receive_data, src/partition_comm.cpp:25-61).
 // Rows are 8-byte multiples; pointers of absent neighbours are null.
+// One exchange can carry the halo rows of up to CN_HALO_PARTS arrays of one row partition (CG
+// needs r and p at once): their rows lie one behind the other in the payload slot.
+#define CN_HALO_PARTS 4
 struct HaloArgs {
-    const char* first_rows = nullptr;  // this rank's first `halo` rows (go to the rank below)
-    const char* last_rows = nullptr;   // this rank's last `halo` rows (go to the rank above)
-    char* halo_below = nullptr;        // local halo rows filled from the rank below
-    char* halo_above = nullptr;        // local halo rows filled from the rank above
+    int nparts = 1;
+    const char* first_rows[CN_HALO_PARTS] = {nullptr};  // this rank's first `halo` rows (go to the rank below)
+    const char* last_rows[CN_HALO_PARTS] = {nullptr};   // this rank's last `halo` rows (go to the rank above)
+    char* halo_below[CN_HALO_PARTS] = {nullptr};        // local halo rows filled from the rank below
+    char* halo_above[CN_HALO_PARTS] = {nullptr};        // local halo rows filled from the rank above
+    size_t bytes[CN_HALO_PARTS] = {0};                  // bytes per direction of each part
     void* me = nullptr;                // this rank's mailbox
     void* box_prev = nullptr;          // mailbox of rank - 1 as mapped here (null: none)
     void* box_next = nullptr;          // mailbox of rank + 1 as mapped here (null: none)
-    size_t bytes = 0;                  // bytes per direction
     // exchanges are counted per neighbour pair (both sides count alike); the parity picks the bank
     unsigned long long epoch_prev = 0, epoch_next = 0;
     unsigned int* ticket = nullptr;    // zeroed block counter, left at zero
