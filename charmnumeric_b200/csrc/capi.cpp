@@ -5,6 +5,7 @@
 
 #include "../../include/cnb200.h"
 #include "context.hpp"
+#include "regions.hpp"
 
 struct cn_context {
     cn::Context impl;
@@ -260,6 +261,45 @@ int cn_fuse_check(const char* node_a, int64_t size_a, const char* node_b, int64_
     return cn::CN_OK;
 }
 
+static cn::Lattice lat(const int64_t* r) { return cn::Lattice{r[0], r[1], r[2]}; }
+
+int cn_region_intersect(const int64_t a[3], const int64_t b[3], int64_t out[3]) {
+    if (!a || !b || !out || a[2] < 1 || b[2] < 1) return cn::CN_ERR_INVALID_ARGUMENT;
+    const cn::Lattice r = cn::lattice_intersect(lat(a), lat(b));
+    out[0] = r.start;
+    out[1] = r.stop;
+    out[2] = r.step;
+    return cn::CN_OK;
+}
+
+int cn_region_map(const int64_t part[3], const int64_t from[3], const int64_t to[3], int64_t out[3]) {
+    if (!part || !from || !to || !out || part[2] < 1 || from[2] < 1 || to[2] < 1) return cn::CN_ERR_INVALID_ARGUMENT;
+    if (part[2] % from[2] != 0 || (part[0] - from[0]) % from[2] != 0 || part[0] < from[0])
+        return cn::CN_ERR_INVALID_ARGUMENT;  // not a sub-lattice of `from`
+    const cn::Lattice r = cn::lattice_map(lat(part), lat(from), lat(to));
+    out[0] = r.start;
+    out[1] = r.stop;
+    out[2] = r.step;
+    return cn::CN_OK;
+}
+
+int cn_plan_row_transfers(const int64_t anchor[3], int64_t anchor_n0, const int64_t leaf[3], int64_t leaf_n0,
+                          int nranks, int64_t* transfers, int64_t cap, int64_t* count, int64_t* iteration_rows) {
+    if (!anchor || !leaf || !count || nranks < 1 || anchor[2] < 1 || leaf[2] < 1 || anchor_n0 < 0 || leaf_n0 < 0)
+        return cn::CN_ERR_INVALID_ARGUMENT;
+    const std::vector<cn::RowTransfer> moves = cn::plan_transfers(lat(anchor), anchor_n0, lat(leaf), leaf_n0, nranks);
+    *count = (int64_t)moves.size();
+    for (int64_t i = 0; transfers && i < *count && i < cap; ++i) {
+        transfers[4 * i + 0] = moves[i].src;
+        transfers[4 * i + 1] = moves[i].dst;
+        transfers[4 * i + 2] = moves[i].lo;
+        transfers[4 * i + 3] = moves[i].hi;
+    }
+    for (int q = 0; iteration_rows && q < nranks; ++q)
+        cn::iteration_rows(lat(anchor), anchor_n0, nranks, q, &iteration_rows[2 * q], &iteration_rows[2 * q + 1]);
+    return cn::CN_OK;
+}
+
 int cn_partition(int64_t n0, int nranks, int rank, int64_t* begin, int64_t* end) {
     if (n0 < 0 || nranks < 1 || rank < 0 || rank >= nranks || !begin || !end)
         return cn::CN_ERR_INVALID_ARGUMENT;
@@ -299,6 +339,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->overlapped_sweeps = s.overlapped_sweeps;
     out->deep_halo_sweeps = s.deep_halo_sweeps;
     out->inlined_producers = s.inlined_producers;
+    out->row_fetches = s.row_fetches;
     return cn::CN_OK;
 }
 

@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "kernels.hpp"
+#include "regions.hpp"
 
 namespace cn {
 
@@ -172,9 +173,7 @@ Array* Context::find(int name) {
 // Slab partition of dimension 0: ceil(n0 / nranks) consecutive rows per rank, the last
 // non-empty rank takes the remainder, ranks beyond it own nothing.
 void slab_partition(int64_t n0, int nranks, int rank, int64_t* begin, int64_t* end) {
-    int64_t per = (n0 + nranks - 1) / nranks;
-    *begin = std::min<int64_t>((int64_t)rank * per, n0);
-    *end = std::min<int64_t>((int64_t)(rank + 1) * per, n0);
+    slab_rows(n0, nranks, rank, begin, end);
 }
 
 void Context::partition(int64_t n0, int64_t* begin, int64_t* end, int r) const {

@@ -22,6 +22,8 @@
 
 namespace cn {
 
+struct Lattice;
+
 struct Buffer {
     void* alloc = nullptr;  // start of the allocation
     char* data = nullptr;   // address of local element (0,0,0)
@@ -94,6 +96,7 @@ struct Stats {
     long long peer_exchanges = 0;    // reductions finished / halos moved through the peer mailboxes
     long long overlapped_sweeps = 0; // stencil sweeps whose interior ran beside the halo exchange
     long long deep_halo_sweeps = 0;  // stencil sweeps that also updated halo rows (no exchange needed next)
+    long long row_fetches = 0;       // operands whose rows were fetched from other ranks for a strided group
     long long inlined_producers = 0; // whole-array assignments folded into the stencil kernel that reads them
 };
 
@@ -212,6 +215,8 @@ private:
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);
     int exchange_halo(Array* a, cudaStream_t st);
+    int fetch_operand_rows(Array* x, const struct Lattice& anchor, int64_t anchor_n0, const struct Lattice& lv, char** data,
+                           int64_t* base_row, std::vector<void*>* fetched);
     int exchange_halos(const std::vector<Array*>& arrays, cudaStream_t st);
     int exchange_halo_p2p(const std::vector<Array*>& arrays, bool has_prev, bool has_next, cudaStream_t st);
     int ensure_second_stream();

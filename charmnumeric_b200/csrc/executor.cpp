@@ -10,6 +10,7 @@
 
 #include "context.hpp"
 #include "kernels.hpp"
+#include "regions.hpp"
 
 namespace cn {
 
@@ -673,6 +674,59 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     return finish_reductions(results, true);
 }
 
+// Rows of operand `x` (view rows `lv`) that this rank reads while it executes its iteration
+// rows of `anchor`, when some of them live on other ranks: every rank takes part, receives what
+// it reads from the others into a scratch copy and sends what the others read of its slab.
+// *data stays null (and *base_row untouched) when every rank reads its own rows only.
+int Context::fetch_operand_rows(Array* x, const Lattice& anchor, int64_t anchor_n0, const Lattice& lv, char** data,
+                                int64_t* base_row, std::vector<void*>* fetched) {
+    *data = nullptr;
+    const std::vector<RowTransfer> moves = plan_transfers(anchor, anchor_n0, lv, x->shape[0], nranks_);
+    if (moves.empty()) return CN_OK;
+    if (!comm_.ready) return fail(CN_ERR_COMM, "moving operand rows between ranks needs cn_comm_init first");
+    for (int r = 0; r < nranks_; ++r)
+        if (failed_[r]) return fail(CN_ERR_RANK_FAILED, "rank " + std::to_string(r) + " was marked failed");
+    const size_t esz = dtype_size(x->dtype);
+    int rc;
+    int64_t lo = 0, hi = 0;
+    rows_read(anchor, anchor_n0, lv, nranks_, rank_, &lo, &hi);
+    char* scratch = nullptr;
+    if (hi > lo) {
+        void* t = nullptr;
+        if ((rc = cuda_fail(cudaMallocAsync(&t, (size_t)(hi - lo) * x->unit * esz + 256, stream_), "operand rows"))) return rc;
+        fetched->push_back(t);
+        scratch = (char*)t;
+        const int64_t o0 = std::max(lo, x->row_begin), o1 = std::min(hi, x->row_end);  // rows this rank owns itself
+        if (o1 > o0)
+            if ((rc = cuda_fail(cudaMemcpyAsync(scratch + (size_t)(o0 - lo) * x->unit * esz,
+                                                x->buf.data + (size_t)(o0 - x->row_begin) * x->unit * esz,
+                                                (size_t)(o1 - o0) * x->unit * esz, cudaMemcpyDeviceToDevice, stream_),
+                                "operand rows")))
+                return rc;
+    }
+    {
+        CommGroup group(&err_);
+        if ((rc = group.started())) return rc;
+        for (const RowTransfer& m : moves) {
+            if (m.dst == rank_)
+                if ((rc = comm_recv(&comm_, scratch + (size_t)(m.lo - lo) * x->unit * esz, (m.hi - m.lo) * x->unit, x->dtype,
+                                    m.src, stream_, &err_)))
+                    return rc;
+            if (m.src == rank_)
+                if ((rc = comm_send(&comm_, x->buf.data + (size_t)(m.lo - x->row_begin) * x->unit * esz,
+                                    (m.hi - m.lo) * x->unit, x->dtype, m.dst, stream_, &err_)))
+                    return rc;
+        }
+        if ((rc = group.end())) return rc;
+    }
+    stats_.row_fetches++;
+    if (scratch) {
+        *data = scratch;
+        *base_row = lo;
+    }
+    return CN_OK;
+}
+
 int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
     const int nd = g.ndims;
     CnGroupArgs a;
@@ -682,41 +736,42 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
     if (rc) return rc;
     if ((int)g.leaves.size() > CN_MAX_IN) return fail(CN_ERR_LIMIT, "too many operands in one group");
 
-    // Along dimension 0 every view must walk the slab in step with the output, otherwise
-    // rows would have to move between ranks.
+    // Iteration rows of this rank.  The anchor is the first output's view (the first operand's
+    // for a group that only reduces): rank q executes the iteration rows whose anchor row lies
+    // in its slab of the anchor array.  An operand whose view is stepped or offset against the
+    // anchor may then read rows that live on other ranks; those rows are fetched into a scratch
+    // copy first (the slab counterpart of send_remote_inputs, src/array_region.hpp:627-663).
     int64_t it_lo = 0, it_hi = g.extent[0];  // iteration rows executed on this rank
+    Lattice anchor;
+    int64_t anchor_n0 = 0;
     if (nranks_ > 1) {
-        const Region* r0 = nullptr;
-        int64_t n0 = -1;
-        auto check = [&](const Region& r, int64_t shape0) {
-            if (r.step[0] != 1) return false;
-            if (!r0) {
-                r0 = &r;
-                n0 = shape0;
-                return true;
-            }
-            return r.start[0] == r0->start[0] && shape0 == n0;
-        };
-        bool ok = true;
-        for (auto& l : g.leaves) ok = ok && check(l.region, l.shape[0]);
-        for (auto& o : g.outs) ok = ok && check(o.region, o.shape[0]);
-        if (!ok)
-            return fail(CN_ERR_UNSUPPORTED,
-                        "a strided group whose views are offset against each other along "
-                        "dimension 0 needs a single rank");
-        if (r0) {
-            int64_t b, e;
-            partition(n0, &b, &e, rank_);
-            it_lo = std::max<int64_t>(0, b - r0->start[0]);
-            it_hi = std::min<int64_t>(g.extent[0], e - r0->start[0]);
-            if (it_hi < it_lo) it_hi = it_lo;
+        const Region* ar = nullptr;
+        if (!g.outs.empty()) {
+            ar = &g.outs[0].region;
+            anchor_n0 = g.outs[0].shape[0];
+        } else if (!g.leaves.empty()) {
+            ar = &g.leaves[0].region;
+            anchor_n0 = g.leaves[0].shape[0];
+        }
+        if (ar) {
+            anchor = Lattice{ar->start[0], ar->stop[0], ar->step[0]};
+            // further outputs have to walk their slabs exactly like the first one
+            for (auto& o : g.outs)
+                if (o.region.start[0] != ar->start[0] || o.region.step[0] != ar->step[0] || o.shape[0] != anchor_n0)
+                    return fail(CN_ERR_UNSUPPORTED,
+                                "outputs of one strided group that are offset against each other along "
+                                "dimension 0 need a single rank");
+            iteration_rows(anchor, anchor_n0, nranks_, rank_, &it_lo, &it_hi);
         }
     }
+    std::vector<void*> fetched;  // scratch copies of operand rows, released after the launch
+    std::vector<char*> leaf_scratch(g.leaves.size(), nullptr);
 
-    auto bind_view = [&](const Array& x, const Region& r, long long* off, long long* str) {
+    // Address of iteration row it_lo of a view: `base_row` is the global row that `data` holds first.
+    auto bind_view = [&](const Array& x, const Region& r, int64_t base_row, long long* off, long long* str) {
         int64_t s[3];
         array_strides(x, s);
-        *off = (r.start[0] + it_lo - x.row_begin) * s[0];
+        *off = (r.start[0] + it_lo * r.step[0] - base_row) * s[0];
         for (int d = 1; d < nd; ++d) *off += r.start[d] * s[d];
         for (int d = 0; d < nd; ++d) str[d] = r.step[d] * s[d];
     };
@@ -727,7 +782,17 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
         if ((rc = check_leaf(x, l.ndims, l.shape, "group operand"))) return rc;
         if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "operand dtype differs from the group dtype");
         a.in[i] = x->buf.data;
-        bind_view(*x, l.region, &a.in_off[i], a.in_str[i]);
+        int64_t base_row = x->row_begin;
+        if (nranks_ > 1 && !x->replicated) {
+            const Lattice lv{l.region.start[0], l.region.stop[0], l.region.step[0]};
+            char* scratch = nullptr;
+            if ((rc = fetch_operand_rows(x, anchor, anchor_n0, lv, &scratch, &base_row, &fetched))) return rc;
+            if (scratch) {
+                a.in[i] = scratch;
+                leaf_scratch[i] = scratch;
+            }
+        }
+        bind_view(*x, l.region, base_row, &a.in_off[i], a.in_str[i]);
     }
     struct Pending {
         Array* target;
@@ -747,7 +812,8 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
             if (x->dtype != g.dtype) return fail(CN_ERR_BAD_DTYPE, "target dtype differs from the group dtype");
         } else {
             if ((rc = create_array(o.name, o.ndims, o.shape, g.dtype, false, &x))) return rc;
-            for (size_t i = 0; i < g.leaves.size(); ++i) a.in[i] = find(g.leaves[i].name)->buf.data;
+            for (size_t i = 0; i < g.leaves.size(); ++i)
+                a.in[i] = leaf_scratch[i] ? leaf_scratch[i] : find(g.leaves[i].name)->buf.data;
         }
         if (o.hazard) {
             // right-hand side reads the target elsewhere: evaluate into a dense temporary
@@ -771,7 +837,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
             copy_back.push_back(p);
         } else {
             a.out[m] = x->buf.data;
-            bind_view(*x, o.region, &a.out_off[m], a.out_str[m]);
+            bind_view(*x, o.region, x->row_begin, &a.out_off[m], a.out_str[m]);
         }
         x->halo_fresh = 0;
     }
@@ -796,7 +862,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
         int64_t s[3];
         array_strides(*x, s);
         const int shift = 3 - nd;
-        dv.off = (p.region.start[0] + it_lo - x->row_begin) * s[0];
+        dv.off = (p.region.start[0] + it_lo * p.region.step[0] - x->row_begin) * s[0];
         for (int d = 1; d < nd; ++d) dv.off += p.region.start[d] * s[d];
         int64_t dense = 1;
         for (int d = nd - 1; d >= 0; --d) {
@@ -811,6 +877,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
         }
         cudaFreeAsync(p.temp.alloc, stream_);
     }
+    for (void* t : fetched) cudaFreeAsync(t, stream_);
     for (auto& sw : swaps) {
         free_buffer(&sw.first->buf);
         sw.first->buf = sw.second;
@@ -913,24 +980,40 @@ int Context::execute_matmul(const AstNode& r) {
         y->halo_fresh = 0;
         return CN_OK;
     }
-    // multi-rank: whole operands only, so that A's and y's row partitions coincide
-    if (ra.start[0] != 0 || ra.start[1] != 0 || rows != A->shape[0] || cols != A->shape[1] ||
-        rx.start[0] != 0 || cols != x->shape[0])
-        return fail(CN_ERR_UNSUPPORTED, "sliced matvec needs a single rank");
+    // Several ranks: y is partitioned like any array of `rows` rows; each rank multiplies the
+    // rows of A[rs:re, cs:ce] that belong to its rows of y.  For whole operands those are its
+    // own rows of A; for a row slice they may live elsewhere and are fetched first (the
+    // reference sends x slices and partial sums instead, src/executor_matmul.cpp:362-390).
+    // x is gathered whole onto every rank.
     if (!comm_.ready) return fail(CN_ERR_COMM, "matvec across ranks needs cn_comm_init first");
-    if ((rc = ensure_scratch((size_t)cols * esz + 256))) return rc;
-    CommGroup group(&err_);
-    if ((rc = group.started())) return rc;
-    for (int p = 0; p < nranks_; ++p) {
-        int64_t b, e;
-        partition(cols, &b, &e, p);
-        if (e <= b) continue;
-        if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * esz, e - b, dtype, p, stream_, &err_))) return rc;
+    const int64_t xlen = x->shape[0];
+    if ((rc = ensure_scratch((size_t)xlen * esz + 256))) return rc;
+    A = find(aname);
+    x = find(xname);
+    y = find(r.result_name);
+    {
+        CommGroup group(&err_);
+        if ((rc = group.started())) return rc;
+        for (int p = 0; p < nranks_; ++p) {
+            int64_t b, e;
+            partition(xlen, &b, &e, p);
+            if (e <= b) continue;
+            if ((rc = comm_broadcast(&comm_, x->buf.data, (char*)scratch_ + b * esz, e - b, dtype, p, stream_, &err_))) return rc;
+        }
+        if ((rc = group.end())) return rc;
     }
-    if ((rc = group.end())) return rc;
-    prof_start("matvec", ((double)A->local_rows() * cols + A->local_rows() + cols) * esz);
-    rc = cuda_fail(launch_matvec(A->buf.data, A->shape[1], scratch_, y->buf.data, A->local_rows(), cols, dtype, stream_), "matvec");
+    const Lattice anchor{0, rows, 1}, arows{ra.start[0], ra.stop[0], 1};
+    std::vector<void*> fetched;
+    char* moved = nullptr;
+    int64_t base_row = A->row_begin;
+    if ((rc = fetch_operand_rows(A, anchor, rows, arows, &moved, &base_row, &fetched))) return rc;
+    const int64_t my_rows = y->local_rows();
+    const char* pa = (moved ? moved : A->buf.data) + ((ra.start[0] + y->row_begin - base_row) * A->shape[1] + ra.start[1]) * esz;
+    const char* px = (const char*)scratch_ + rx.start[0] * esz;
+    prof_start("matvec", ((double)my_rows * cols + my_rows + cols) * esz);
+    rc = cuda_fail(launch_matvec(pa, A->shape[1], px, y->buf.data, my_rows, cols, dtype, stream_), "matvec");
     prof_stop();
+    for (void* t : fetched) cudaFreeAsync(t, stream_);
     if (rc) return rc;
     stats_.kernel_launches++;
     y->halo_fresh = 0;

@@ -146,6 +146,22 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
 int cn_fuse_check(const char* node_a, int64_t size_a, const char* node_b, int64_t size_b,
                   char* source, int64_t cap, int* fused, char* err, int errcap);
 
+/* Host-only region algebra of the slab planner, on (start, stop, step) triples of row indices.
+ * cn_region_intersect: common rows of two stepped regions (ArrayRegion intersect,
+ * src/array_region.hpp:136-222).  cn_region_map: `part` is a piece of view `from`; the result is
+ * the piece of view `to` at the same positions (map, src/array_region.hpp:461-536, pinned by
+ * tests/test_jit.cpp:301-326).  cn_plan_row_transfers: a group iterates over `anchor` (the view
+ * of its first output, an array of anchor_n0 rows) and reads `leaf` (a view of an array of
+ * leaf_n0 rows); rank q executes the iteration rows whose anchor row it owns
+ * (iteration_rows[2q], [2q+1], optional) and every (src, dst, row_lo, row_hi) quadruple in
+ * `transfers` is a block of operand rows that has to travel (local_inputs /
+ * send_remote_inputs, src/array_region.hpp:553-663). */
+int cn_region_intersect(const int64_t a[3], const int64_t b[3], int64_t out[3]);
+int cn_region_map(const int64_t part[3], const int64_t from[3], const int64_t to[3], int64_t out[3]);
+int cn_plan_row_transfers(const int64_t anchor[3], int64_t anchor_n0, const int64_t leaf[3],
+                          int64_t leaf_n0, int nranks, int64_t* transfers, int64_t cap,
+                          int64_t* count, int64_t* iteration_rows);
+
 /* Rows [*begin, *end) of dimension 0 that `rank` of `nranks` owns for an array with n0 rows
  * (host-only).  Takes the place of the reference's tile -> chare map
  * (ArrayDecomp::owning_chare / chare_region_global, src/array_region.hpp:357-368): here one
@@ -199,6 +215,7 @@ typedef struct cn_stats {
     int64_t overlapped_sweeps; /* stencil sweeps whose interior ran beside the halo exchange */
     int64_t deep_halo_sweeps;  /* stencil sweeps that also updated halo rows (see option "halo") */
     int64_t inlined_producers; /* whole-array assignments folded into the stencil kernel behind them */
+    int64_t row_fetches;       /* operands of strided groups whose rows were fetched from other ranks */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 

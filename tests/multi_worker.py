@@ -51,7 +51,9 @@ def main():
         A = cnp.random.uniform((301, 128), seed=21, low=-1.0, high=1.0)
         x = cnp.random.uniform((128,), seed=22, low=-1.0, high=1.0)
         y = A @ x
-        return {"y": y, "n": y @ y}
+        # a row / column slice: the rows of A behind a rank's rows of the result live on other ranks
+        ys = A[30:250, 16:100].matvec(x[16:100])
+        return {"y": y, "n": y @ y, "ys": ys}
 
     def diag():
         n = 75
@@ -80,6 +82,9 @@ def main():
             x, xn = xn, x
         return {"x": x, "xn": xn}
     progs["jacobi2d_pingpong"] = pingpong
+    import __graft_entry__ as entry_points
+    progs["multigrid"] = entry_points._multigrid(65, 91)
+    progs["cg_rotated"] = entry_points._cg_rotated(70, 34, 9)
     progs["chain"] = chain
     progs["diag"] = diag
     progs["tile"] = tile
@@ -111,6 +116,8 @@ def main():
     result["peer_exchanges"] = np.array(st["peer_exchanges"])
     result["overlapped_sweeps"] = np.array(st["overlapped_sweeps"])
     result["deep_halo_sweeps"] = np.array(st["deep_halo_sweeps"])
+    result["row_fetches"] = np.array(st["row_fetches"])
+    result["inlined_producers"] = np.array(st["inlined_producers"])
     np.savez(os.path.join(outdir, f"{case}_rank{rank}.npz"), **result)
     itf.close()
 

@@ -72,6 +72,31 @@ def test_multi_gpu_matches_oracle(tmp_path, case, nranks):
     _check(case, _run_ranks(tmp_path, case, nranks, 1), 1)
 
 
+@pytest.mark.parametrize("nranks,p2p", [(2, 1), (2, 0), (4, 1)])
+def test_multi_gpu_stepped_views_across_slabs(tmp_path, nranks, p2p):
+    """A multigrid V-cycle and red-black Gauss-Seidel sweeps: restriction, prolongation and the
+    coloured sweeps read and write every second row, so operand rows travel between ranks."""
+    if _gpu_count() < nranks:
+        pytest.skip(f"needs {nranks} GPUs")
+    results = _run_ranks(tmp_path, "multigrid", nranks, p2p)
+    for r, d in enumerate(results):
+        for key in ("u", "g"):
+            assert d["gpu_" + key].tobytes() == d["cpu_" + key].tobytes(), (r, key)
+        assert int(d["row_fetches"]) > 0
+
+
+@pytest.mark.parametrize("nranks", [2, 4])
+def test_multi_gpu_cg_direction_update_inlined(tmp_path, nranks):
+    """CG entered at the direction update: the fused kernel reads r and p one row beyond the
+    slab, both halos travel in one exchange."""
+    if _gpu_count() < nranks:
+        pytest.skip(f"needs {nranks} GPUs")
+    results = _run_ranks(tmp_path, "cg_rotated", nranks, 1)
+    _check("cg", results, 1)
+    for d in results:
+        assert int(d["inlined_producers"]) == 9
+
+
 @pytest.mark.parametrize("case", ["jacobi2d", "jacobi3d", "cg", "chain"])
 def test_multi_gpu_nccl_transport(tmp_path, case):
     """The same programs with the peer mailboxes switched off: NCCL moves halos and totals."""
