@@ -676,6 +676,22 @@ int Context::execute_node(const Dag& dag, size_t* index) {
         ++*index;
         return CN_OK;
     }
+    // an assignment whose source has another rank (or its singleton dimensions elsewhere)
+    if (node.roots.size() == 1 && node.roots[0]->opcode == OP_SET_REGION && node.roots[0]->operands.size() == 2) {
+        const AstNode& r = *node.roots[0];
+        const Operand& rhs = r.operands[1];
+        if (!rhs.is_ref && rhs.leaf && r.operands[0].leaf && !rhs.leaf->is_scalar && !rhs.leaf->is_broadcast) {
+            const AstNode& tl = *r.operands[0].leaf;
+            const Region sreg = rhs.region.is_global ? Region::full(rhs.leaf->ndims, rhs.leaf->shape) : rhs.region;
+            const Region treg = r.region.is_global ? Region::full(tl.ndims, tl.shape) : r.region;
+            bool same = sreg.ndims == treg.ndims;
+            for (int d = 0; same && d < sreg.ndims; ++d) same = sreg.extent(d) == treg.extent(d);
+            if (!same && sreg.size() > 1) {
+                ++*index;
+                return execute_cross_set_region(r);
+            }
+        }
+    }
     if (is_group_node(node)) {
         // REDUCE / SUM nodes that directly follow a group may be folded into its kernel
         auto scan_reductions = [&](size_t from, size_t* end) {

@@ -211,6 +211,7 @@ private:
     int execute_matmul(const AstNode& root);
     int execute_randu(const AstNode& root);
     int execute_diag(const AstNode& root);
+    int execute_cross_set_region(const AstNode& root);
     int execute_tile(const AstNode& root);
     int execute_create(const AstNode& root);
     int try_plain_fill(const DagNode& node, bool* done);

@@ -1020,6 +1020,109 @@ int Context::execute_matmul(const AstNode& r) {
     return CN_OK;
 }
 
+// Cross-dimension SET_REGION (execute_cross_set_region_node, src/executor_transfer.cpp:66-177):
+// the assigned region and the source view have different ranks, or carry their singleton
+// dimensions in different places -- `A[i, :] = v`, `v[:] = A[:, j]`, `H[t, :, k:] = prev`.  The
+// dimensions of extent > 1 of both sides are matched in order (the reference's dim_map); the
+// assignment is then one strided copy.  With several ranks the source rows are either aligned
+// with the target rows through the row lattices (both sides iterate over their dimension 0
+// together), or the source region is gathered whole onto every rank first.
+int Context::execute_cross_set_region(const AstNode& r) {
+    if (r.operands.size() != 2 || !r.operands[0].leaf) return fail(CN_ERR_BAD_BLOB, "SET_REGION needs (target, rhs)");
+    Array* t = find(r.operands[0].leaf->result_name);
+    if (!t) return fail(CN_ERR_UNKNOWN_ARRAY, "SET_REGION target " + std::to_string(r.operands[0].leaf->result_name) + " does not exist");
+    Array* src = nullptr;
+    Region sreg;
+    int rc = operand_array(r.operands[1], &src, &sreg);
+    if (rc) return rc;
+    if (src->dtype != t->dtype) return fail(CN_ERR_BAD_DTYPE, "SET_REGION source dtype differs from the target");
+    if (src->name == t->name) return fail(CN_ERR_HAZARD, "cross-dimension SET_REGION of an array into itself");
+    Region treg = r.region.is_global ? Region::full(t->ndims, t->shape) : r.region;
+    if (treg.ndims != t->ndims) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION region rank differs from target");
+    for (int d = 0; d < t->ndims; ++d)
+        if (treg.stop[d] > t->shape[d] || treg.start[d] > treg.stop[d]) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION region outside its target");
+    // dimensions of extent > 1, matched in order
+    int map[kMaxDims] = {-1, -1, -1};  // target dim -> source dim
+    std::vector<int> td, sd;
+    for (int d = 0; d < t->ndims; ++d)
+        if (treg.extent(d) > 1) td.push_back(d);
+    for (int d = 0; d < src->ndims; ++d)
+        if (sreg.extent(d) > 1) sd.push_back(d);
+    if (td.size() != sd.size()) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION source and region do not have the same non-singleton dimensions");
+    for (size_t i = 0; i < td.size(); ++i) {
+        if (treg.extent(td[i]) != sreg.extent(sd[i])) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION source does not match the region shape");
+        map[td[i]] = sd[i];
+    }
+    if (treg.size() == 0) return CN_OK;
+    if (treg.size() != sreg.size()) return fail(CN_ERR_SHAPE_MISMATCH, "SET_REGION source does not match the region shape");
+    const size_t esz = dtype_size(t->dtype);
+    int64_t ts[3], ss[3];
+    array_strides(*t, ts);
+    array_strides(*src, ss);
+    // target rows of the region on this rank: positions [i0, i1) along the region's dimension 0
+    const Lattice trows{treg.start[0], treg.stop[0], treg.step[0]};
+    int64_t i0 = 0, i1 = treg.extent(0);
+    if (nranks_ > 1 && !t->replicated) iteration_rows(trows, t->shape[0], nranks_, rank_, &i0, &i1);
+    const char* sdata = src->buf.data;
+    int64_t sbase = src->row_begin;  // global row that sdata holds first
+    std::vector<void*> fetched;
+    const bool row_aligned = map[0] == 0;  // both sides walk their dimension 0 together
+    if (nranks_ > 1 && !src->replicated) {
+        if (!comm_.ready) return fail(CN_ERR_COMM, "SET_REGION across ranks needs cn_comm_init first");
+        if (row_aligned && !t->replicated) {
+            char* moved = nullptr;
+            const Lattice srows{sreg.start[0], sreg.stop[0], sreg.step[0]};
+            if ((rc = fetch_operand_rows(src, trows, t->shape[0], srows, &moved, &sbase, &fetched))) return rc;
+            if (moved) sdata = moved;
+        } else {
+            // every rank gets the rows of the source region: [sreg.start[0], sreg.stop[0])
+            const int64_t g0 = sreg.start[0], g1 = sreg.stop[0];
+            if ((rc = ensure_scratch((size_t)(g1 - g0) * src->unit * esz + 256))) return rc;
+            t = find(r.operands[0].leaf->result_name);
+            src = find(r.operands[1].leaf->result_name);
+            CommGroup group(&err_);
+            if ((rc = group.started())) return rc;
+            for (int p = 0; p < nranks_; ++p) {
+                int64_t b, e;
+                partition(src->shape[0], &b, &e, p);
+                const int64_t o0 = std::max(b, g0), o1 = std::min(e, g1);
+                if (o1 <= o0) continue;
+                const char* mine = src->buf.data + (size_t)(o0 - src->row_begin) * src->unit * esz;
+                char* const landing = (char*)scratch_ + (size_t)(o0 - g0) * src->unit * esz;
+                if ((rc = comm_broadcast(&comm_, p == rank_ ? mine : landing, landing,
+                                         (o1 - o0) * src->unit, src->dtype, p, stream_, &err_)))
+                    return rc;
+            }
+            if ((rc = group.end())) return rc;
+            sdata = (const char*)scratch_;
+            sbase = g0;
+        }
+    }
+    if (i1 > i0) {
+        StridedView dv, sv;
+        int64_t ext[3] = {1, 1, 1};
+        const int shift = 3 - t->ndims;
+        dv.off = (treg.start[0] + i0 * treg.step[0] - t->row_begin) * ts[0];
+        for (int d = 1; d < t->ndims; ++d) dv.off += treg.start[d] * ts[d];
+        // source element of region position 0 along every dimension, rows counted from sbase
+        sv.off = (sreg.start[0] - sbase) * ss[0];
+        for (int d = 1; d < src->ndims; ++d) sv.off += sreg.start[d] * ss[d];
+        for (int d = 0; d < t->ndims; ++d) {
+            ext[shift + d] = d == 0 ? i1 - i0 : treg.extent(d);
+            dv.str[shift + d] = treg.step[d] * ts[d];
+            sv.str[shift + d] = map[d] >= 0 ? sreg.step[map[d]] * ss[map[d]] : 0;
+        }
+        // the target's dimension 0 starts at position i0: advance the source along the dimension it maps to
+        if (map[0] >= 0) sv.off += i0 * sreg.step[map[0]] * ss[map[0]];
+        rc = cuda_fail(launch_copy_region(t->buf.data, dv, sdata, sv, ext, t->dtype, stream_), "cross-dimension copy");
+        if (rc) return rc;
+        stats_.kernel_launches++;
+    }
+    for (void* p : fetched) cudaFreeAsync(p, stream_);
+    t->halo_fresh = 0;
+    return CN_OK;
+}
+
 // DIAG (src/execute_node.cpp:600-750): a vector becomes the k-th diagonal of a zeroed square
 // matrix, or the k-th diagonal of a matrix becomes a vector.  Both are one strided copy.
 // With k = 0 (and rows <= cols for the extraction) the row partition of the matrix and the

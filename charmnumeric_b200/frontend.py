@@ -128,7 +128,7 @@ class _Op:
     __slots__ = ("kind", "opcode", "result", "operands", "region", "payload")
 
     def __init__(self, kind, opcode=None, result=None, operands=(), region=None, payload=None):
-        self.kind = kind          # "ew", "set", "create", "reduce", "sum", "matmul", "diag", "tile", "randu", "put"
+        self.kind = kind          # "ew", "set", "xset" (cross-dimension assignment), "create", "reduce", "sum", "matmul", "diag", "tile", "randu", "put"
         self.opcode = opcode
         self.result = result      # _Info
         self.operands = list(operands)  # (_Info, Region | None) or python scalar
@@ -351,8 +351,16 @@ class _ArrayOps:
         rhs = _coerce_assignment(rhs, region.shape(), self.dtype)
         if isinstance(rhs, _ArrayOps):
             if tuple(rhs.shape) != tuple(region.shape()) and rhs.size != 1:
-                raise ValueError(f"could not broadcast input from shape {rhs.shape} "
-                                 f"into shape {region.shape()}")
+                # the same elements with the singleton dimensions elsewhere (`A[i, :] = v`,
+                # `v[:] = A[:, j]`): a cross-dimension assignment, its own node
+                # (src/executor_transfer.cpp:66-177)
+                if [d for d in rhs.shape if d != 1] != [d for d in region.shape() if d != 1]:
+                    raise ValueError(f"could not broadcast input from shape {rhs.shape} "
+                                     f"into shape {region.shape()}")
+                if rhs.dtype != self.dtype:
+                    raise TypeError("cross-dimension assignment needs matching dtypes")
+                _record(_Op("xset", wire.OP_SET_REGION, self._info, [rhs._operand()], region=region))
+                return
             operand = rhs._operand()
         else:
             operand = rhs
@@ -934,6 +942,13 @@ def _single_node(op):
         root = wire.Ast(res.name, wire.OP_DIAG, shape=res.shape, dtype=dt,
                         operands=[(_leaf(i), r) for i, r in op.operands]
                         + [(wire.scalar(float(op.payload)), None)])
+    elif op.kind == "xset":
+        src, sreg = op.operands[0]
+        root = wire.Ast(_state.new_name(), wire.OP_SET_REGION, shape=tuple(op.region.shape()), dtype=dt,
+                        region=op.region, operands=[(_leaf(res), None), (_leaf(src), sreg)])
+        node = wire.Node(_state.next_node, [root], fusible=False)
+        _state.next_node += 1
+        return node
     elif op.kind == "randu":
         root = wire.Ast(res.name, wire.OP_RANDU, shape=res.shape, dtype=dt,
                         operands=[(wire.scalar(v), None) for v in op.operands])
@@ -986,7 +1001,7 @@ def build_nodes(ops):
         for op in seg_ops:
             for info, _ in _op_views(op):
                 readers.setdefault(info.name, set()).add(si)
-            if op.kind == "set":
+            if op.kind in ("set", "xset"):
                 # the target of an assignment has to exist as an array, even when the program
                 # drops its last handle on it before the batch is built
                 readers.setdefault(op.result.name, set()).add(si)
@@ -1039,7 +1054,7 @@ def execute(interface, mirror=None):
     _state.dead.clear()
     for op in ops:
         res = op.result
-        if res is not None and op.kind != "set" and res.materialised and not res.alive \
+        if res is not None and op.kind not in ("set", "xset") and res.materialised and not res.alive \
                 and res.name not in dead:
             dead.append(res.name)
     flush(dead)

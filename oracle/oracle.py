@@ -237,6 +237,11 @@ class Oracle:
                 if target.size == 1 and r.region is None:
                     target.reshape(-1)[0] = rhs.reshape(-1)[0]
                 else:
+                    dest = target[_slices(r.region, target.shape)]
+                    if rhs.shape != dest.shape and rhs.size == dest.size and rhs.size > 1:
+                        # cross-dimension assignment (src/executor_transfer.cpp:66-177): the same
+                        # elements in the same order, singleton dimensions placed differently
+                        rhs = rhs.reshape(dest.shape)
                     target[_slices(r.region, target.shape)] = rhs
             elif op == OP_REDUCE:
                 a = self._operand(r.operands[0], values, dtype)

@@ -85,6 +85,7 @@ def main():
     import __graft_entry__ as entry_points
     progs["multigrid"] = entry_points._multigrid(65, 91)
     progs["cg_rotated"] = entry_points._cg_rotated(70, 34, 9)
+    progs["xset"] = G._cross_dimension_program
     progs["chain"] = chain
     progs["diag"] = diag
     progs["tile"] = tile

@@ -86,6 +86,19 @@ def test_multi_gpu_stepped_views_across_slabs(tmp_path, nranks, p2p):
 
 
 @pytest.mark.parametrize("nranks", [2, 4])
+def test_multi_gpu_cross_dimension_assignment(tmp_path, nranks):
+    """Rows into columns, columns into vectors, planes of a 3-D array: the source region is
+    either row-aligned with the target or gathered onto every rank."""
+    if _gpu_count() < nranks:
+        pytest.skip(f"needs {nranks} GPUs")
+    results = _run_ranks(tmp_path, "xset", nranks, 1)
+    for r, d in enumerate(results):
+        for key in d.files:
+            if key.startswith("gpu_"):
+                assert d[key].tobytes() == d["cpu_" + key[4:]].tobytes(), (r, key)
+
+
+@pytest.mark.parametrize("nranks", [2, 4])
 def test_multi_gpu_cg_direction_update_inlined(tmp_path, nranks):
     """CG entered at the direction update: the fused kernel reads r and p one row beyond the
     slab, both halos travel in one exchange."""

@@ -534,3 +534,36 @@ def test_producer_not_inlined_when_the_stencil_overwrites_its_input(interface):
     after = interface.context.stats()
     assert after["inlined_producers"] == before["inlined_producers"]
     assert_bit_exact(gpu, cpu)
+
+
+# ---- cross-dimension SET_REGION (src/executor_transfer.cpp:66-177) ------------------------------
+
+def _cross_dimension_program():
+    A = cnp.random.uniform((37, 22), seed=61)
+    v = cnp.random.uniform((22,), seed=62)
+    c = cnp.random.uniform((37,), seed=63)
+    w = cnp.zeros((37,))
+    row = cnp.zeros((22,))
+    A[5, :] = v                 # 1-D into a row
+    A[:, 3] = c                 # 1-D into a column
+    w[:] = A[:, 7]              # a column into 1-D
+    row[:] = A[30, :]           # a row into 1-D
+    H = cnp.zeros((6, 37, 22))
+    H[2, :, 4:] = A[:, 4:]      # 2-D into a plane of a 3-D array (examples/lstm_forward.py:36)
+    B = cnp.zeros((37, 22))
+    B[1:36:2, :] = H[2, 1:36:2, :]   # a stepped plane back into 2-D
+    col = cnp.zeros((37, 1))
+    col[:, :] = c               # (n,) into (n, 1)
+    return {"A": A, "w": w, "row": row, "H": H, "B": B, "col": col}
+
+
+def test_cross_dimension_assignment(interface):
+    gpu, cpu = run_both(interface, _cross_dimension_program)
+    assert_bit_exact(gpu, cpu)
+
+
+def test_cross_dimension_assignment_rejects_mismatched_shapes():
+    a = cnp.zeros((5, 6))
+    v = cnp.zeros((5,))
+    with pytest.raises(ValueError):
+        a[2, :] = v
