@@ -30,6 +30,12 @@ class Stats(C.Structure):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
 
 
+class ArrayMeta(C.Structure):
+    """cn_array_meta of include/cnb200.h."""
+    _fields_ = [("name", C.c_int32), ("ndims", C.c_int32), ("shape", C.c_int64 * 3), ("offset", C.c_int64 * 3),
+                ("tile", C.c_int64), ("decomp_final", C.c_int32), ("reserved", C.c_int32)]
+
+
 # symbol -> (restype, argtypes); must list every function include/cnb200.h declares
 _P = C.c_void_p
 _I64P = C.POINTER(C.c_int64)
@@ -67,6 +73,8 @@ SIGNATURES = {
     "cn_region_map": (C.c_int, [_I64P, _I64P, _I64P, _I64P]),
     "cn_plan_row_transfers": (C.c_int, [_I64P, C.c_int64, _I64P, C.c_int64, C.c_int, _I64P, C.c_int64,
                                         _I64P, _I64P]),
+    "cn_compute_decompositions": (C.c_int, [C.POINTER(ArrayMeta), C.c_int, C.c_char_p, C.c_int64, C.c_int, C.c_int,
+                                            _I64P]),
     "cn_partition": (C.c_int, [C.c_int64, C.c_int, C.c_int, _I64P, _I64P]),
     "cn_timer_start": (C.c_int, [_P]),
     "cn_timer_stop": (C.c_int, [_P, C.POINTER(C.c_float)]),

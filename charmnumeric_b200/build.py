@@ -17,7 +17,7 @@ OUT = HERE / "libcnb200.so"
 BUILD = HERE / "_build"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-HOST_SOURCES = ["wire.cpp", "lower.cpp", "fuse.cpp", "regions.cpp", "codegen.cpp", "jit.cpp", "comm.cpp", "context.cpp",
+HOST_SOURCES = ["wire.cpp", "lower.cpp", "fuse.cpp", "regions.cpp", "decomp.cpp", "codegen.cpp", "jit.cpp", "comm.cpp", "context.cpp",
                 "executor.cpp", "capi.cpp"]
 CUDA_SOURCES = ["kernels.cu", "noalloc.cu"]
 

@@ -162,6 +162,27 @@ int cn_plan_row_transfers(const int64_t anchor[3], int64_t anchor_n0, const int6
                           int64_t leaf_n0, int nranks, int64_t* transfers, int64_t cap,
                           int64_t* count, int64_t* iteration_rows);
 
+/* Host-only: tile sizes and alignment offsets for the arrays a DAG creates, so that their tiles
+ * line up with the tiles of the arrays they are computed from or stored into.  Stands in for
+ * decomposition_solver::compute_decompositions(array_meta, dag, odf, num_pes)
+ * (src/decomposition_solver.hpp:95; known answers: tests/test_compute_decompositions.cpp:128-396).
+ * `arrays` is read and updated in place: entries with decomp_final != 0 are fixed, the others
+ * receive a tile, an offset per dimension and decomp_final = 1 when the DAG relates them to a
+ * fixed array.  `dag_blob` is a CNB1 blob (may be NULL: tiles only); `min_tile` gives the
+ * minimum tile of 1-D / 2-D / 3-D arrays (NULL: 262144 / 512 / 64, src/backend.hpp:15-17).
+ * The slab executor itself needs no per-array offsets; this is for hosts that keep tile grids. */
+typedef struct cn_array_meta {
+    int32_t name;
+    int32_t ndims;
+    int64_t shape[3];
+    int64_t offset[3];
+    int64_t tile;
+    int32_t decomp_final;
+    int32_t reserved;
+} cn_array_meta;
+int cn_compute_decompositions(cn_array_meta* arrays, int n_arrays, const char* dag_blob,
+                              int64_t size, int odf, int num_pes, const int64_t min_tile[3]);
+
 /* Rows [*begin, *end) of dimension 0 that `rank` of `nranks` owns for an array with n0 rows
  * (host-only).  Takes the place of the reference's tile -> chare map
  * (ArrayDecomp::owning_chare / chare_region_global, src/array_region.hpp:357-368): here one
