@@ -1126,8 +1126,8 @@ int Context::execute_cross_set_region(const AstNode& r) {
 // DIAG (src/execute_node.cpp:600-750): a vector becomes the k-th diagonal of a zeroed square
 // matrix, or the k-th diagonal of a matrix becomes a vector.  Both are one strided copy.
 // With k = 0 (and rows <= cols for the extraction) the row partition of the matrix and the
-// partition of the vector coincide, so the copy is local on every rank; other cases need the
-// general redistribution and run on one rank only.
+// partition of the vector coincide, so the copy is local on every rank; with an offset the
+// rows behind a rank's part of the result are fetched from their owners first.
 int Context::execute_diag(const AstNode& r) {
     if (r.operands.size() != 2) return fail(CN_ERR_BAD_BLOB, "DIAG needs (array, k)");
     const Operand& kop = r.operands[1];
@@ -1143,41 +1143,69 @@ int Context::execute_diag(const AstNode& r) {
     if (r.result_name == v->name) return fail(CN_ERR_HAZARD, "DIAG result aliases its operand");
     const int64_t roff = k < 0 ? -k : 0, coff = k > 0 ? k : 0;
     const int vname = v->name, dtype = v->dtype;
+    const size_t esz = dtype_size(dtype);
     Array* out = nullptr;
     StridedView dv, sv;
     int64_t ext[3] = {1, 1, 0};
+    const char* sdata = nullptr;
+    std::vector<void*> fetched;
     if (v->ndims == 1) {
+        // out[i + roff, i + coff] = v[i]: this rank fills the diagonal entries of its own rows
         const int64_t len = v->shape[0], n = len + roff + coff;
-        if (nranks_ > 1 && k != 0) return fail(CN_ERR_UNSUPPORTED, "DIAG with an offset needs a single rank");
         int64_t shape[2] = {n, n};
         if ((rc = create_array(r.result_name, 2, shape, dtype, true, &out))) return rc;
         v = find(vname);
-        ext[2] = v->local_rows();
-        sv.off = 0;
+        int64_t i0 = 0, i1 = len;  // positions along the diagonal whose row this rank owns
+        const Lattice orows{roff, roff + len, 1}, vrows{0, len, 1};
+        int64_t vbase = v->row_begin;
+        sdata = v->buf.data;
+        if (nranks_ > 1) {
+            iteration_rows(orows, n, nranks_, rank_, &i0, &i1);
+            char* moved = nullptr;
+            if ((rc = fetch_operand_rows(v, orows, n, vrows, &moved, &vbase, &fetched))) return rc;
+            out = find(r.result_name);
+            v = find(vname);
+            if (moved) sdata = moved;
+            else sdata = v->buf.data;
+        }
+        ext[2] = i1 - i0;
+        sv.off = i0 - vbase;
         sv.str[2] = 1;
-        dv.off = (v->row_begin + roff - out->row_begin) * n + v->row_begin + coff;
+        dv.off = (i0 + roff - out->row_begin) * n + i0 + coff;
         dv.str[2] = n + 1;
     } else if (v->ndims == 2) {
+        // d[i] = M[i + roff, i + coff]: this rank fills its own entries of d
         const int64_t rows = v->shape[0], cols = v->shape[1];
         const int64_t len = k >= 0 ? std::min(rows, cols - k) : std::min(rows + k, cols);
         if (len <= 0) return fail(CN_ERR_SHAPE_MISMATCH, "DIAG offset outside the matrix");
-        if (nranks_ > 1 && (k != 0 || rows > cols)) return fail(CN_ERR_UNSUPPORTED, "this DIAG extraction needs a single rank");
         int64_t shape[1] = {len};
         if ((rc = create_array(r.result_name, 1, shape, dtype, false, &out))) return rc;
         v = find(vname);
+        const Lattice drows{0, len, 1}, mrows{roff, roff + len, 1};
+        int64_t mbase = v->row_begin;
+        sdata = v->buf.data;
+        if (nranks_ > 1) {
+            char* moved = nullptr;
+            if ((rc = fetch_operand_rows(v, drows, len, mrows, &moved, &mbase, &fetched))) return rc;
+            out = find(r.result_name);
+            v = find(vname);
+            sdata = moved ? moved : v->buf.data;
+        }
         ext[2] = out->local_rows();
         dv.off = 0;
         dv.str[2] = 1;
-        sv.off = (out->row_begin + roff - v->row_begin) * cols + out->row_begin + coff;
+        sv.off = (out->row_begin + roff - mbase) * cols + out->row_begin + coff;
         sv.str[2] = cols + 1;
     } else {
         return fail(CN_ERR_UNSUPPORTED, "DIAG needs a 1-D or 2-D array");
     }
     if (ext[2] > 0) {
-        rc = cuda_fail(launch_copy_region(out->buf.data, dv, v->buf.data, sv, ext, dtype, stream_), "diag");
+        rc = cuda_fail(launch_copy_region(out->buf.data, dv, sdata, sv, ext, dtype, stream_), "diag");
         if (rc) return rc;
         stats_.kernel_launches++;
     }
+    for (void* p : fetched) cudaFreeAsync(p, stream_);
+    (void)esz;
     out->halo_fresh = 0;
     return CN_OK;
 }

@@ -60,7 +60,12 @@ def main():
         A = cnp.random.uniform((n, n), seed=31, low=-1.0, high=1.0) + cnp.diag(cnp.full((n,), 2.0 * n))
         d = cnp.diag(A)
         x = cnp.random.uniform((n,), seed=32)
-        return {"A": A, "d": d, "x1": x + (1.0 / d) * (cnp.ones((n,)) - A @ x)}
+        tall = cnp.random.uniform((90, 40), seed=33)
+        return {"A": A, "d": d, "x1": x + (1.0 / d) * (cnp.ones((n,)) - A @ x),
+                # diagonals off the main one, and of a tall matrix: the rows behind a rank's part
+                # of the result live on other ranks
+                "up": cnp.diag(x, 2), "down": cnp.diag(x, -5), "d_up": cnp.diag(A, 3), "d_down": cnp.diag(A, -7),
+                "d_tall": cnp.diag(tall), "d_tall_down": cnp.diag(tall, -30)}
 
     def tile():
         h0 = cnp.random.uniform((37,), seed=41)
