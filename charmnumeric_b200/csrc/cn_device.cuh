@@ -59,6 +59,8 @@ struct
     void* red[CN_MAX_RED];       // reduction results (size-1 arrays)
     long long nzc, zchunk;       // staged 3-D kernels: number and length of the z chunks marched
     long long tm_off[3];         // staged kernels: local coordinate -> descriptor coordinate offset
+    long long own_lo, own_hi;    // rows (planes) of dimension 0 this rank owns: reductions count those only,
+                                 // also when the sweep is widened into the halo rows
     long long fill_lo[2], fill_hi[2];  // staged producers: local rows / columns of the producer's inputs that hold data
     unsigned int* error;         // device error word (set when a bounded wait runs out)
     // fused cross-GPU reduction: every rank's mailbox as mapped on this GPU (peer_n = 0: off)

@@ -385,7 +385,7 @@ struct Gen {
                 std::string prod = rd.b.kind == ValRef::NONE
                                        ? "(ACC)" + val(rd.a, e)
                                        : "(ACC)(" + val(rd.a, e) + " * " + val(rd.b, e) + ")";
-                o << ind << "if (" << guard(rd.domain, e) << ") acc" << q << " += " << prod
+                o << ind << "if (" << guard(rd.domain, e) << (nd() >= 2 ? " & ownr" : "") << ") acc" << q << " += " << prod
                   << ";\n";
             }
         }
@@ -470,6 +470,9 @@ struct Gen {
                 if (!fast) o << "      if (y >= a.hi[" << (N - 2) << "]) break;\n";
                 if (N == 2) o << "      const long long p = y * s0 + x;\n";
                 else o << "      const long long p = z * s0 + y * s1 + x;\n";
+                if (!g.reds.empty())
+                    o << "      const bool ownr = (" << (N == 2 ? "y" : "z") << " >= a.own_lo) & (" << (N == 2 ? "y" : "z")
+                      << " < a.own_hi);\n";
             }
             emit_guards(fast);
             if (fast && N == 1) o << "      {\n";
@@ -749,6 +752,9 @@ struct Gen {
             if (N == 2) o << "        const long long p = y * s0 + x;\n";
             else o << "        const long long p = z * s0 + y * s1 + x;\n";
             o << "        const int sq = (ly * CN_R + r + CN_HY) * CN_SW + lx * 2;\n";
+            if (!g.reds.empty())
+                o << "        const bool ownr = (" << (N == 2 ? "y" : "z") << " >= a.own_lo) & (" << (N == 2 ? "y" : "z")
+                  << " < a.own_hi);\n";
             emit_guards(fast);
             if (fast) o << "        if (x < xhi) {\n";
             else o << "        if " << guard_any(DOM_BOX) << " {\n";

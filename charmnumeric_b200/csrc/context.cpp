@@ -3,6 +3,8 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <vector>
 
 #include "kernels.hpp"
@@ -13,6 +15,13 @@ namespace cn {
 namespace {
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Mailboxes that outlived their context.  A mailbox is exported over CUDA IPC and another rank
+// may still hold a mapping of it when this rank's context goes away, so it is never freed; the
+// next context created on the same device in this process takes it over instead of allocating
+// another 64 MiB.
+std::mutex g_box_mutex;
+std::map<int, std::vector<void*>> g_spare_boxes;  // device -> mailboxes ready for reuse
 
 }  // namespace
 
@@ -36,7 +45,7 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_DEEP_HALO")) deep_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_HALO")) {
         int v = atoi(f);
-        if (v >= 0 && v <= 8) halo_ = v;
+        if (v >= 0 && v <= 32) halo_ = v;
     }
     staged_tile_.tx = 64;
     staged_tile_.r = 4;
@@ -72,8 +81,10 @@ Context::~Context() {
         for (int p = 0; p < nranks_; ++p)
             if (p != rank_ && peer_.box[p]) cudaIpcCloseMemHandle(peer_.box[p]);
         cudaFree(peer_.ticket);
-        // peer_.mine is not freed here: another rank may still hold a mapping of it, and
-        // freeing exported memory under a live mapping is undefined; it goes with the process
+        // peer_.mine is not freed: another rank may still hold a mapping of it, and freeing
+        // exported memory under a live mapping is undefined; the next context on this device reuses it
+        std::lock_guard<std::mutex> lock(g_box_mutex);
+        g_spare_boxes[device_].push_back(peer_.mine);
     }
     if (stream2_) {
         cudaStreamSynchronize(stream2_);
@@ -308,7 +319,16 @@ int Context::setup_peer_boxes() {
     cudaIpcMemHandle_t mine_h;
     memset(&mine_h, 0, sizeof(mine_h));
     if (ok) {
-        if (cudaMalloc(&peer_.mine, box_bytes) != cudaSuccess || cudaMemset(peer_.mine, 0, sizeof(CnPeerBox)) != cudaSuccess ||
+        {
+            std::lock_guard<std::mutex> lock(g_box_mutex);
+            std::vector<void*>& spare = g_spare_boxes[device_];
+            if (!spare.empty()) {
+                peer_.mine = spare.back();
+                spare.pop_back();
+            }
+        }
+        if ((!peer_.mine && cudaMalloc(&peer_.mine, box_bytes) != cudaSuccess) ||
+            cudaMemset(peer_.mine, 0, sizeof(CnPeerBox)) != cudaSuccess ||
             cudaIpcGetMemHandle(&mine_h, peer_.mine) != cudaSuccess) {
             cudaGetLastError();
             ok = 0;
@@ -357,8 +377,12 @@ int Context::setup_peer_boxes() {
         for (int p = 0; p < nranks_; ++p)
             if (p != rank_ && peer_.box[p]) cudaIpcCloseMemHandle(peer_.box[p]);
         // another rank may have mapped this rank's mailbox before the vote failed; freeing
-        // exported memory under a live mapping is undefined, so it stays until the process ends
+        // exported memory under a live mapping is undefined, so it is kept for the next context
         if (peer_.ticket) cudaFree(peer_.ticket);
+        if (peer_.mine) {
+            std::lock_guard<std::mutex> lock(g_box_mutex);
+            g_spare_boxes[device_].push_back(peer_.mine);
+        }
         peer_ = PeerState();
     }
     return CN_OK;

@@ -422,7 +422,8 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         // With a halo deeper than the stencil's reach a sweep can also update rows of the halo
         // itself (the neighbour computes the same values for its own rows), so that the next
         // sweeps need no exchange: one exchange of `halo` rows serves up to halo / reach sweeps.
-        if (deep_halo_ && halo_ > 1 && g.reds.empty() && g.souts.empty() && !g.flat && !prod && ref->row_end > ref->row_begin) {
+        // (a fused reduction does not stand in the way: it counts the rank's own rows only)
+        if (deep_halo_ && halo_ > 1 && g.souts.empty() && !g.flat && !prod && ref->row_end > ref->row_begin) {
             int64_t e = halo_;
             for (size_t i = 0; i < ins.size(); ++i) {
                 const bool refreshed = std::find(stale.begin(), stale.end(), ins[i]) != stale.end();
@@ -465,6 +466,8 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
     // local rows, widened by `ext` towards every neighbour that exists (the global box clips at
     // the physical edges of the array by itself)
     const int64_t wb = rb - (rb > 0 ? ext : 0), we = re + (re < ref->shape[0] ? ext : 0);
+    a.own_lo = 0;
+    a.own_hi = re - rb;
     lo[0] = std::max(lo[0], wb) - rb;
     hi[0] = std::min(hi[0], we) - rb;
     rlo[0] = std::max(rlo[0], wb) - rb;

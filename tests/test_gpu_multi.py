@@ -133,7 +133,7 @@ def test_multi_gpu_overlapped_halo(tmp_path, case):
 @pytest.mark.parametrize("case,halo,p2p,nranks", [
     ("jacobi2d_long", 4, 1, 2), ("jacobi2d_long", 3, 0, 2), ("jacobi3d_long", 4, 1, 2), ("cg", 4, 1, 2),
     ("jacobi3d_long", 2, 1, 2), ("jacobi2d_long", 4, 1, 4), ("jacobi3d_long", 2, 1, 4),
-    ("jacobi2d_pingpong", 4, 1, 2), ("jacobi2d_pingpong", 4, 0, 2)])
+    ("jacobi2d_pingpong", 4, 1, 2), ("jacobi2d_pingpong", 4, 0, 2), ("jacobi2d_long", 16, 1, 2)])
 def test_multi_gpu_deep_halo(tmp_path, case, halo, p2p, nranks):
     """Halo depth above the stencil's reach: sweeps also update halo rows (redundantly with the
     neighbour), so one exchange serves several sweeps.  Results stay bit-exact."""
