@@ -413,7 +413,8 @@ def measure(name, args, itf, dist, rank, world, local_rank, primary):
     # ---- device-timed region: repeated bursts of K steps ----
     stats0 = ctx.stats()
     t_begin = datetime.datetime.now()
-    times, step_index = timed_bursts(ctx, dist, wl, K, step_index, 5, 1200.0 if primary else 800.0)
+    times, step_index = timed_bursts(ctx, dist, wl, K, step_index, 5,
+                                     0.0 if args.quick else (1200.0 if primary else 800.0), max_bursts=4000)
     ctx.synchronize()
     t_end = datetime.datetime.now()
     stats1 = ctx.stats()
@@ -570,6 +571,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--scale", type=float, default=1.0, help="linear problem-size factor (1 = the configured size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true",
+                    help="five timed bursts only (profiling runs); the clock sampler may then see too little load")
     ap.add_argument("--no-check", action="store_true", help="skip the untimed parity check against the oracle")
     ap.add_argument("--halo", type=int, default=0, help="halo rows per side for N > 1 (0: per-workload default)")
     args = ap.parse_args()
