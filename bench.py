@@ -332,12 +332,18 @@ def run_reference(args, rank, world):
 def timed_bursts(ctx, dist, wl, K, step_index, min_bursts, min_total_ms, max_bursts=400):
     """Bursts of K steps, each bracketed by a barrier and a device synchronisation and timed
     with CUDA events on the library's stream (maximum over ranks).  Every rank sees the same
-    maxima, so all ranks run the same number of bursts."""
+    maxima, so all ranks run the same number of bursts.  On several ranks a device-side barrier
+    (one allreduce of one value) is enqueued in front of each burst's start event."""
     times = []
     total = 0.0
+    align = wl.align_blob() if dist is not None else None
     while len(times) < min_bursts or (total < min_total_ms and len(times) < max_bursts):
         barrier(dist)
         ctx.synchronize()
+        if align is not None:
+            # a one-value allreduce in front of the start event: the ranks leave the host barrier
+            # tens of microseconds apart, which a burst of 13 us steps would otherwise count
+            ctx.receive_dag(align)
         ctx.timer_start()
         for _ in range(K):
             wl.run_step(step_index)

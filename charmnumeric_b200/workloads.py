@@ -55,6 +55,20 @@ class Workload:
         self.points = d["points"]                  # grid points / elements / matrix entries per step (all ranks)
         self.bytes_per_step = d["bytes_per_step"]  # algorithmic HBM bytes per step, all ranks
         self.description = d["description"]
+        self._result_host = None
+        self._align_src = F.zeros((8,))  # created by the subclass's first execute
+        self._align_blob = None
+
+    def align_blob(self):
+        """A DAG whose only work is a sum over a tiny array: on several ranks that is one
+        allreduce, i.e. a barrier on the devices.  Submitted right before a timed burst it lines
+        the ranks' streams up, so that the burst does not start with one GPU waiting for the
+        others to be given their work."""
+        if self._align_blob is None:
+            def record():
+                self.keep.append(F.sum_all(self._align_src))
+            self._align_blob = wire.dag_blob(_capture_step(record))
+        return self._align_blob
 
     @classmethod
     def describe(cls, nranks=1, scale=1.0):
@@ -85,7 +99,12 @@ class Workload:
         self.ctx.receive_dag(self.blobs[self.pick(i)])
 
     def read_result(self):
-        return float(self.ctx.get(self.result.name)[0])
+        """The step's size-1 result, read back into a host buffer that is allocated once."""
+        if self._result_host is None:
+            import numpy as np
+            self._result_host = np.zeros((1,), dtype=np.float64)
+        self.ctx.get_into(self.result.name, self._result_host)
+        return float(self._result_host[0])
 
 
 class CG(Workload):
