@@ -24,7 +24,7 @@ class Stats(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
         "kernel_launches", "group_launches", "compiles", "halo_exchanges", "allreduces",
         "fused_reductions", "nodes", "bytes_h2d", "bytes_d2h", "plan_hits", "peer_exchanges", "overlapped_sweeps", "deep_halo_sweeps",
-        "inlined_producers", "row_fetches")]
+        "inlined_producers", "row_fetches", "halo_pushes")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}

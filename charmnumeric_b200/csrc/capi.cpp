@@ -340,6 +340,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->deep_halo_sweeps = s.deep_halo_sweeps;
     out->inlined_producers = s.inlined_producers;
     out->row_fetches = s.row_fetches;
+    out->halo_pushes = s.halo_pushes;
     return cn::CN_OK;
 }
 
@@ -367,6 +368,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
         return ctx->impl.debug_peer_wait();
     } else if (k == "p2p") {
         ctx->impl.set_p2p(value != 0);
+    } else if (k == "push_halo") {
+        ctx->impl.set_push_halo(value != 0);
     } else if (k == "fuse_producers") {
         if (value < 0 || value > 2) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_fuse_producers((int)value);

@@ -61,6 +61,14 @@ struct
     long long tm_off[3];         // staged kernels: local coordinate -> descriptor coordinate offset
     long long own_lo, own_hi;    // rows (planes) of dimension 0 this rank owns: reductions count those only,
                                  // also when the sweep is widened into the halo rows
+    // edge rows pushed by the producing kernel: outputs in push_mask also store their first
+    // push_elems elements (the rows next to rank - 1) at push_prev and their last push_elems
+    // elements (starting at local element push_last) at push_next, both in the neighbours'
+    // mailboxes (null: no such neighbour); one array per output slot
+    void* push_prev[CN_MAX_OUT];
+    void* push_next[CN_MAX_OUT];
+    long long push_elems, push_last;
+    unsigned int push_mask, push_pad;
     long long fill_lo[2], fill_hi[2];  // staged producers: local rows / columns of the producer's inputs that hold data
     unsigned int* error;         // device error word (set when a bounded wait runs out)
     // fused cross-GPU reduction: every rank's mailbox as mapped on this GPU (peer_n = 0: off)

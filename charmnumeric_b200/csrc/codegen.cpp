@@ -122,6 +122,11 @@ struct Gen {
         o << "  }\n";
     }
 
+    // stores into other GPUs' mailboxes are made visible there before the kernel ends
+    void push_fence() {
+        o << "#if CN_PUSH\n  if (a.push_mask) __threadfence_system();\n#endif\n";
+    }
+
     void red_decl() {
         for (size_t i = 0; i < g.reds.size(); ++i) o << "  ACC acc" << i << " = (ACC)0;\n";
     }
@@ -377,6 +382,21 @@ struct Gen {
             } else {
                 o << ind << "if (" << guard(dom, 0) << ") out" << m << "[p] = w" << m << "_0;\n";
             }
+            // the slab's edge rows also go straight into the neighbours' mailboxes
+            o << "#if CN_PUSH\n";
+            o << ind << "if (a.push_mask & " << (1u << m) << "u) {\n";
+            for (int e = 0; e < V; ++e) {
+                o << ind << "  if (" << guard(dom, e) << ") {\n";
+                o << ind << "    const unsigned long long q = (unsigned long long)(p + " << e << ");\n";
+                o << ind << "    if (a.push_prev[" << m << "] && q < (unsigned long long)a.push_elems) ((T*)a.push_prev[" << m
+                  << "])[q] = w" << m << "_" << e << ";\n";
+                o << ind << "    const unsigned long long t = q - (unsigned long long)a.push_last;\n";
+                o << ind << "    if (a.push_next[" << m << "] && t < (unsigned long long)a.push_elems) ((T*)a.push_next[" << m
+                  << "])[t] = w" << m << "_" << e << ";\n";
+                o << ind << "  }\n";
+            }
+            o << ind << "}\n";
+            o << "#endif\n";
         }
         // reductions
         for (size_t q = 0; q < g.reds.size(); ++q) {
@@ -581,6 +601,7 @@ struct Gen {
         emit_rows(false);
         o << "    }\n";
         o << "  }\n";
+        push_fence();
         red_epilogue();
         o << "}\n";
     }
@@ -904,6 +925,7 @@ struct Gen {
             o << "  }\n";
         }
         o << "  if (timed_out && a.error) atomicExch(a.error, 1u);\n";
+        push_fence();
         red_epilogue();
         o << "}\n";
     }

@@ -38,6 +38,7 @@ Context::Context(int device, int rank, int nranks)
     }
     if (const char* f = getenv("CN_FUSE_REDUCTIONS")) fuse_reductions_ = atoi(f) != 0;
     if (const char* f = getenv("CN_FLAT_PREFETCH")) flat_prefetch_ = std::max(-1, std::min(2, atoi(f)));
+    if (const char* f = getenv("CN_PUSH_HALO")) push_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_FUSE_PRODUCERS")) fuse_producers_ = std::max(0, std::min(2, atoi(f)));
     if (const char* f = getenv("CN_STENCIL_SHFL")) stencil_shfl_ = atoi(f) != 0;
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
@@ -226,7 +227,7 @@ int Context::create_array(int name, int ndims, const int64_t* shape, int dtype, 
             if (zero) {
                 int rc = cuda_fail(cudaMemsetAsync(old->buf.alloc, 0, old->buf.bytes, stream_), "memset");
                 if (rc) return rc;
-                old->halo_fresh = 0;
+                old->mark_written();
             }
             if (out) *out = old;
             return CN_OK;
@@ -473,6 +474,21 @@ int Context::exchange_halo(Array* a, cudaStream_t st) {
 // payload slot together travel in ONE peer-store launch (CG's fused kernel needs r and p: one
 // exchange latency instead of two); anything else goes array by array.
 int Context::exchange_halos(const std::vector<Array*>& arrays, cudaStream_t st) {
+    // remember who asks together: the kernels that produce these arrays next will push their
+    // edge rows themselves, into one payload slot
+    if (!arrays.empty() && arrays.size() <= CN_HALO_PARTS) {
+        std::vector<int> names;
+        for (Array* a : arrays) {
+            a->halo_wanted = true;
+            names.push_back(a->name);
+        }
+        if (names != halo_group_) halo_group_ = names;
+    }
+    // rows that the producing kernels pushed already: publish, wait, copy in
+    if (pending_.active) {
+        int rc = pull_pending(st);
+        if (rc) return rc;
+    }
     std::vector<Array*> todo;
     for (Array* a : arrays)
         if (!(nranks_ == 1 || a->replicated || (a->halo > 0 && a->halo_fresh == a->halo))) todo.push_back(a);
@@ -512,6 +528,53 @@ int Context::exchange_halos(const std::vector<Array*>& arrays, cudaStream_t st) 
         int rc = exchange_halo(a, st);
         if (rc) return rc;
     }
+    return CN_OK;
+}
+
+// The second half of an exchange whose first half (this rank's edge rows into the neighbours'
+// mailboxes) was done by the kernels that produced the rows: publish them with the epoch,
+// wait (bounded) for the neighbours' rows of the same epoch and copy those into the halo rows
+// of every array whose pushed version is still the current one.
+int Context::pull_pending(cudaStream_t st) {
+    if (!pending_.active) return CN_OK;
+    pending_.active = false;
+    HaloArgs h;
+    h.pull_only = true;
+    h.nparts = (int)pending_.names.size();
+    std::vector<Array*> installed;
+    double total = 0;
+    for (size_t q = 0; q < pending_.names.size(); ++q) {
+        h.bytes[q] = pending_.bytes[q];
+        Array* a = find(pending_.names[q]);
+        const size_t esz = a ? dtype_size(a->dtype) : 8;
+        if (!a || !a->halo_pushed || (size_t)a->halo * a->unit * esz != pending_.bytes[q]) continue;  // overwritten since
+        const int64_t nl = a->local_rows();
+        h.halo_below[q] = a->buf.data - pending_.bytes[q];
+        h.halo_above[q] = a->buf.data + (size_t)nl * a->unit * esz;
+        installed.push_back(a);
+        total += (double)pending_.bytes[q];
+    }
+    h.epoch_prev = pending_.epoch_prev;
+    h.epoch_next = pending_.epoch_next;
+    h.me = peer_.mine;
+    h.box_prev = pending_.has_prev ? peer_.box[rank_ - 1] : nullptr;
+    h.box_next = pending_.has_next ? peer_.box[rank_ + 1] : nullptr;
+    h.ticket = peer_.ticket;
+    h.error = error_word_;
+    if (h.box_prev || h.box_next) {
+        prof_start("halo pull (rows pushed by their producers)", total * ((h.box_prev ? 1 : 0) + (h.box_next ? 1 : 0)), st);
+        int rc = cuda_fail(launch_halo_exchange(h, sm_count_, st), "halo pull");
+        prof_stop();
+        if (rc) return rc;
+        stats_.kernel_launches++;
+        waiting_launches_++;
+        stats_.peer_exchanges++;
+    }
+    for (Array* a : installed) {
+        a->halo_fresh = a->halo;
+        a->halo_pushed = false;
+    }
+    stats_.halo_exchanges++;
     return CN_OK;
 }
 
@@ -906,7 +969,7 @@ int Context::try_plain_fill(const DagNode& node, bool* done) {
             if (rc) return rc;
             stats_.kernel_launches++;
         }
-        a->halo_fresh = 0;
+        a->mark_written();
     }
     *done = true;
     return CN_OK;

@@ -41,6 +41,14 @@ struct Array {
     int halo = 0;                        // halo rows allocated on each side
     Buffer buf, shadow;
     int halo_fresh = 0;  // halo rows (per side) that hold the neighbours' current values, 0..halo
+    bool halo_pushed = false;  // the producing kernel stored the current edge rows into the neighbours' mailboxes
+    bool halo_wanted = false;  // a stencil has asked for this array's halo before: worth pushing
+
+    // the array's own rows changed by a path that neither widens nor pushes: the halo is stale
+    void mark_written() {
+        halo_fresh = 0;
+        halo_pushed = false;
+    }
 
     int64_t local_rows() const { return row_end - row_begin; }
     int64_t local_elems() const { return local_rows() * unit; }
@@ -96,6 +104,7 @@ struct Stats {
     long long peer_exchanges = 0;    // reductions finished / halos moved through the peer mailboxes
     long long overlapped_sweeps = 0; // stencil sweeps whose interior ran beside the halo exchange
     long long deep_halo_sweeps = 0;  // stencil sweeps that also updated halo rows (no exchange needed next)
+    long long halo_pushes = 0;       // kernels that stored their edge rows into the neighbours' mailboxes themselves
     long long row_fetches = 0;       // operands whose rows were fetched from other ranks for a strided group
     long long inlined_producers = 0; // whole-array assignments folded into the stencil kernel that reads them
 };
@@ -176,7 +185,8 @@ public:
     void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
     void set_overlap_halo(bool on) { overlap_halo_ = on; }
     void set_deep_halo(bool on) { deep_halo_ = on; }
-    void set_p2p(bool on) { p2p_wanted_ = on; }  // takes effect at cn_comm_init
+    void set_p2p(bool on) { p2p_wanted_ = on; }
+    void set_push_halo(bool on) { push_halo_ = on; plans_.clear(); }  // takes effect at cn_comm_init
     bool p2p_ready() const { return peer_.ready; }
 
 private:
@@ -219,6 +229,9 @@ private:
     int fetch_operand_rows(Array* x, const struct Lattice& anchor, int64_t anchor_n0, const struct Lattice& lv, char** data,
                            int64_t* base_row, std::vector<void*>* fetched);
     int exchange_halos(const std::vector<Array*>& arrays, cudaStream_t st);
+    int pull_pending(cudaStream_t st);
+    void plan_push(const GroupIR& g, const std::vector<Array*>& outs, int64_t ext, CnGroupArgs* a,
+                   std::vector<Array*>* pushed);
     int exchange_halo_p2p(const std::vector<Array*>& arrays, bool has_prev, bool has_next, cudaStream_t st);
     int ensure_second_stream();
     int setup_peer_boxes();
@@ -266,6 +279,18 @@ private:
         unsigned long long epoch_prev = 0, epoch_next = 0;  // halo exchanges with rank - 1 / rank + 1
         unsigned int* ticket = nullptr;       // block counter of the halo kernel
     } peer_;
+    // Edge rows pushed by the kernels that produced them (one exchange epoch, up to CN_HALO_PARTS
+    // arrays), waiting for the small kernel that publishes them, waits for the neighbours' and
+    // copies those into the local halo rows.
+    struct PendingPush {
+        bool active = false;
+        std::vector<int> names;     // arrays of the group, in payload order
+        std::vector<size_t> bytes;  // halo bytes per direction of each
+        bool has_prev = false, has_next = false;
+        unsigned long long epoch_prev = 0, epoch_next = 0;
+    } pending_;
+    std::vector<int> halo_group_;   // arrays whose halos were last asked for together
+    bool push_halo_ = false;        // option "push_halo": measured slower than the stand-alone exchange, off
     bool p2p_wanted_ = true;
     long long waiting_launches_ = 0;          // launches that contain a bounded wait (TMA, peers)
     long long checked_launches_ = 0;          // of which already covered by an error-word check

@@ -58,6 +58,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     }
     tile.drop_copies = g.staged && debug_drop_copies_;
     tile.shfl = stencil_shfl_ && g.cls == GroupIR::SHIFTED && !g.flat && !g.staged;
+    tile.push = push_halo_ && nranks_ > 1 && peer_.ready && g.cls == GroupIR::SHIFTED && !overlap_halo_;
     // heavy flat groups issue the loads of all their rows before the arithmetic: between the
     // out-of-line slow paths of exp / sqrt / division the compiler leaves each row's loads
     // next to their use, and the memory system idles while a row is computed (measured on the
@@ -67,7 +68,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
                       std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
                       "|mb" + std::to_string(tile.minb) + "|fu" + std::to_string(tile.fill_u) +
-                      "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "");
+                      "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "") + (tile.push ? "|push" : "");
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -600,6 +601,8 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         for (size_t m = 0; m < outs.size(); ++m) outs[m] = find(g.outs[m].name);
     }
 
+    std::vector<Array*> pushed;
+    if (k->tile.push && ntiles > 0 && !overlap) plan_push(g, outs, ext, &a, &pushed);
     if (ntiles > 0 || !g.reds.empty() || !g.souts.empty()) {
         // algorithmic bytes: every distinct array read once, every output written once
         double vol = 1;
@@ -668,6 +671,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
             if (!whole) fresh = std::min(fresh, x->halo_fresh);
         }
         x->halo_fresh = fresh;
+        x->halo_pushed = std::find(pushed.begin(), pushed.end(), x) != pushed.end();
     }
     if (ext > 0) stats_.deep_halo_sweeps++;
     for (auto& sw : swaps) {
@@ -675,6 +679,98 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         sw.first->buf = sw.second;
     }
     return finish_reductions(results, true);
+}
+
+// Which outputs of this launch store their edge rows into the neighbours' mailboxes
+// themselves.  An output qualifies when a stencil has asked for its halo before, the launch
+// leaves its halo stale (no widening), it writes whole rows, and it belongs to the group of
+// arrays whose halos were last asked for together (their rows share one exchange epoch and lie
+// one behind the other in the payload slot).  The rows are published and the neighbours'
+// copied in by pull_pending(), when a stencil asks for them.
+void Context::plan_push(const GroupIR& g, const std::vector<Array*>& outs, int64_t ext, CnGroupArgs* a,
+                        std::vector<Array*>* pushed) {
+    if (ext != 0 || !peer_.ready || halo_group_.empty()) return;
+    for (size_t m = 0; m < outs.size() && m < CN_MAX_OUT; ++m) {
+        Array* x = outs[m];
+        const OutIR& o = g.outs[m];
+        if (!x->halo_wanted || x->replicated || x->halo <= 0) continue;
+        const auto part = std::find(halo_group_.begin(), halo_group_.end(), x->name);
+        if (part == halo_group_.end()) continue;
+        // every element of the edge rows has to come out of this kernel
+        const bool through = g.copy_through && o.hazard;
+        bool whole_rows = g.flat || through;
+        if (!whole_rows) {
+            whole_rows = !(g.two_domains && o.domain == DOM_REGION);
+            for (int d = 1; d < g.ndims; ++d) whole_rows = whole_rows && g.box_lo[d] <= 0 && g.box_hi[d] >= x->shape[d];
+            whole_rows = whole_rows && g.box_lo[0] <= x->row_begin && g.box_hi[0] >= x->row_end;
+        }
+        if (!whole_rows) continue;
+        const size_t esz = dtype_size(x->dtype);
+        const int64_t nl = x->local_rows();
+        const size_t bytes = (size_t)x->halo * x->unit * esz;
+        if (nl < x->halo || bytes % 8) continue;
+        int64_t b, e;
+        bool has_prev = false, has_next = false, thin = false;
+        if (nl > 0 && rank_ > 0) {
+            partition(x->shape[0], &b, &e, rank_ - 1);
+            has_prev = e > b;
+            thin = thin || (has_prev && e - b < x->halo);
+        }
+        if (nl > 0 && rank_ + 1 < nranks_) {
+            partition(x->shape[0], &b, &e, rank_ + 1);
+            has_next = e > b;
+            thin = thin || (has_next && e - b < x->halo);
+        }
+        // every rank has to come to the same decision: no slab anywhere may be thinner than the halo
+        for (int q = 0; q < nranks_ && !thin; ++q) {
+            partition(x->shape[0], &b, &e, q);
+            thin = e > b && e - b < x->halo;
+        }
+        if (thin) continue;
+        // payload layout of the group: every member's rows, 16-byte aligned, in group order
+        std::vector<size_t> sizes;
+        size_t total = 0, offset = 0;
+        bool fits = true;
+        for (int name : halo_group_) {
+            Array* y = find(name);
+            if (!y || y->shape[0] != x->shape[0] || y->halo != x->halo || y->replicated) {
+                fits = false;
+                break;
+            }
+            const size_t sz = (size_t)y->halo * y->unit * dtype_size(y->dtype);
+            if (name == x->name) offset = total;
+            sizes.push_back(sz);
+            total += (sz + 15) & ~(size_t)15;
+        }
+        if (!fits || total > CN_PEER_HALO_SLOT) continue;
+        // one epoch at a time: rows of another group, or an earlier version of this array,
+        // are published and pulled first
+        if (pending_.active && (pending_.names != halo_group_ || x->halo_pushed)) {
+            if (pull_pending(stream_) != CN_OK) return;
+        }
+        if (!pending_.active) {
+            pending_ = PendingPush();
+            pending_.active = true;
+            pending_.names = halo_group_;
+            pending_.bytes = sizes;
+            pending_.has_prev = has_prev;
+            pending_.has_next = has_next;
+            if (has_prev) pending_.epoch_prev = ++peer_.epoch_prev;
+            if (has_next) pending_.epoch_next = ++peer_.epoch_next;
+        } else if (pending_.has_prev != has_prev || pending_.has_next != has_next) {
+            continue;
+        }
+        const int bp = (int)(pending_.epoch_prev & 1ULL), bn = (int)(pending_.epoch_next & 1ULL);
+        char* const base_prev = has_prev ? (char*)peer_.box[rank_ - 1] + sizeof(CnPeerBox) + (size_t)(bp * 2 + 1) * CN_PEER_HALO_SLOT : nullptr;
+        char* const base_next = has_next ? (char*)peer_.box[rank_ + 1] + sizeof(CnPeerBox) + (size_t)(bn * 2 + 0) * CN_PEER_HALO_SLOT : nullptr;
+        a->push_prev[m] = base_prev ? base_prev + offset : nullptr;
+        a->push_next[m] = base_next ? base_next + offset : nullptr;
+        a->push_elems = (long long)x->halo * x->unit;
+        a->push_last = (long long)(nl - x->halo) * x->unit;
+        a->push_mask |= 1u << m;
+        pushed->push_back(x);
+        stats_.halo_pushes++;
+    }
 }
 
 // Rows of operand `x` (view rows `lv`) that this rank reads while it executes its iteration
@@ -842,7 +938,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
             a.out[m] = x->buf.data;
             bind_view(*x, o.region, x->row_begin, &a.out_off[m], a.out_str[m]);
         }
-        x->halo_fresh = 0;
+        x->mark_written();
     }
     for (int d = 0; d < 3; ++d) a.ext[d] = d < nd ? ext[d] : 1;
     int64_t total = 1;
@@ -980,7 +1076,7 @@ int Context::execute_matmul(const AstNode& r) {
         prof_stop();
         if (rc) return rc;
         stats_.kernel_launches++;
-        y->halo_fresh = 0;
+        y->mark_written();
         return CN_OK;
     }
     // Several ranks: y is partitioned like any array of `rows` rows; each rank multiplies the
@@ -1019,7 +1115,7 @@ int Context::execute_matmul(const AstNode& r) {
     for (void* t : fetched) cudaFreeAsync(t, stream_);
     if (rc) return rc;
     stats_.kernel_launches++;
-    y->halo_fresh = 0;
+    y->mark_written();
     return CN_OK;
 }
 
@@ -1122,7 +1218,7 @@ int Context::execute_cross_set_region(const AstNode& r) {
         stats_.kernel_launches++;
     }
     for (void* p : fetched) cudaFreeAsync(p, stream_);
-    t->halo_fresh = 0;
+    t->mark_written();
     return CN_OK;
 }
 
@@ -1209,7 +1305,7 @@ int Context::execute_diag(const AstNode& r) {
     }
     for (void* p : fetched) cudaFreeAsync(p, stream_);
     (void)esz;
-    out->halo_fresh = 0;
+    out->mark_written();
     return CN_OK;
 }
 
@@ -1266,7 +1362,7 @@ int Context::execute_tile(const AstNode& r) {
     rc = cuda_fail(launch_tile(out->buf.data, oshape, out->row_begin, out->local_rows(), src, sshape, dtype, stream_), "tile");
     if (rc) return rc;
     stats_.kernel_launches++;
-    out->halo_fresh = 0;
+    out->mark_written();
     return CN_OK;
 }
 
@@ -1289,7 +1385,7 @@ int Context::execute_randu(const AstNode& r) {
                                 (uint64_t)v[0], v[1], v[2], stream_), "randu");
     if (rc) return rc;
     stats_.kernel_launches++;
-    x->halo_fresh = 0;
+    x->mark_written();
     return CN_OK;
 }
 
@@ -1441,7 +1537,7 @@ int Context::put(int name, int ndims, const int64_t* shape, int dtype, const voi
         if ((rc = cuda_fail(cudaMemcpyAsync(x->buf.data, src, bytes, cudaMemcpyHostToDevice, stream_), "put copy"))) return rc;
         stats_.bytes_h2d += bytes;
     }
-    x->halo_fresh = 0;
+    x->mark_written();
     return CN_OK;
 }
 
@@ -1459,7 +1555,7 @@ int Context::put_local(int name, int ndims, const int64_t* shape, int dtype, int
         if ((rc = cuda_fail(cudaMemcpyAsync(x->buf.data, host_slab, bytes, cudaMemcpyHostToDevice, stream_), "put copy"))) return rc;
         stats_.bytes_h2d += bytes;
     }
-    x->halo_fresh = 0;
+    x->mark_written();
     return CN_OK;
 }
 

@@ -97,6 +97,7 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
                           d_s1.c_str(),                 d_ns.c_str(),
                           d_mb.c_str(),                 d_fu.c_str(),
                           d_pf.c_str(),                 tile.shfl ? "-DCN_SHFL=1" : "-DCN_SHFL=0",
+                          tile.push ? "-DCN_PUSH=1" : "-DCN_PUSH=0",
                           tile.drop_copies ? "-DCN_DEBUG_DROP_COPIES=1" : "-DCN_DEBUG_DROP_COPIES=0",
                           tile.drop_copies ? "-DCN_WAIT_LIMIT=2000u" : "-DCN_WAIT_LIMIT=2000000u"};
     rc = api->CompileProgram(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);

@@ -29,6 +29,9 @@ struct TileConfig {
     // stencil kernels: single neighbours along the last dimension come from the neighbour
     // lanes' registers (warp shuffle) instead of their own loads
     bool shfl = false;
+    // kernels of a multi-rank context can store their slab's edge rows into the neighbours'
+    // mailboxes themselves (the launch arguments say when)
+    bool push = false;
     int minb = 1;    // resident blocks per SM the compiler has to leave room for (register cap)
     int fill_u = 3;  // staged producers: points per thread whose loads are issued together
 };

@@ -410,7 +410,7 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_
     __shared__ int arrived;
     const int bp = (int)(h.epoch_prev & 1ULL), bn = (int)(h.epoch_next & 1ULL);
     // rows for the rank below arrive there "from above" (dir 1), and the other way round
-    {
+    if (!h.pull_only) {
         size_t off = 0;
         for (int q = 0; q < h.nparts; ++q) {
             if (h.box_prev) halo_copy(halo_slot(h.box_prev, bp, 1) + off, h.first_rows[q], h.bytes[q], vec_push != 0);
@@ -423,14 +423,18 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_
     // before its ticket; the release stores of the last ticket holder then publish everything.
     if (threadIdx.x == 0) {
         int last = 1;
-        if (gridDim.x > 1) {
+        if (h.pull_only) {
+            // the payload was stored and fenced by earlier kernels of this stream
+            last = blockIdx.x == 0 ? 1 : 0;
+            if (last) __threadfence_system();
+        } else if (gridDim.x > 1) {
             __threadfence_system();
             last = atomicAdd(h.ticket, 1u) == gridDim.x - 1 ? 1 : 0;
         }
         if (last) {
             if (h.box_prev) cn_st_release_sys(&((CnPeerBox*)h.box_prev)->halo_flag[bp][1], h.epoch_prev);
             if (h.box_next) cn_st_release_sys(&((CnPeerBox*)h.box_next)->halo_flag[bn][0], h.epoch_next);
-            if (gridDim.x > 1) *h.ticket = 0u;
+            if (gridDim.x > 1 && !h.pull_only) *h.ticket = 0u;
         }
         CnPeerBox* me = (CnPeerBox*)h.me;
         bool ok = true;
@@ -444,8 +448,8 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(HaloArgs h, int vec_
     if (!arrived) return;
     size_t off = 0;
     for (int q = 0; q < h.nparts; ++q) {
-        if (h.box_prev) halo_unpack(h.halo_below[q], halo_slot(h.me, bp, 0) + off, h.bytes[q], vec_pull != 0);
-        if (h.box_next) halo_unpack(h.halo_above[q], halo_slot(h.me, bn, 1) + off, h.bytes[q], vec_pull != 0);
+        if (h.box_prev && h.halo_below[q]) halo_unpack(h.halo_below[q], halo_slot(h.me, bp, 0) + off, h.bytes[q], vec_pull != 0);
+        if (h.box_next && h.halo_above[q]) halo_unpack(h.halo_above[q], halo_slot(h.me, bn, 1) + off, h.bytes[q], vec_pull != 0);
         off += (h.bytes[q] + 15) & ~(size_t)15;
     }
 }
@@ -460,7 +464,8 @@ cudaError_t launch_halo_exchange(const HaloArgs& h, int sm_count, cudaStream_t s
         if (h.bytes[q] % 8) return cudaErrorInvalidValue;
         total += (h.bytes[q] + 15) & ~(size_t)15;
         largest = std::max(largest, h.bytes[q]);
-        vec_push = vec_push && h.bytes[q] % 16 == 0 && (((uintptr_t)h.first_rows[q] | (uintptr_t)h.last_rows[q]) & 15) == 0;
+        vec_push = vec_push && !h.pull_only && h.bytes[q] % 16 == 0 &&
+                   (((uintptr_t)h.first_rows[q] | (uintptr_t)h.last_rows[q]) & 15) == 0;
         vec_pull = vec_pull && h.bytes[q] % 16 == 0 && (((uintptr_t)h.halo_below[q] | (uintptr_t)h.halo_above[q]) & 15) == 0;
     }
     if (largest == 0 || (!h.box_prev && !h.box_next)) return cudaSuccess;

@@ -58,6 +58,10 @@ struct HaloArgs {
     unsigned int* ticket = nullptr;    // zeroed block counter, left at zero
     unsigned int* error = nullptr;     // device error word
     unsigned int wait_limit = 0;       // polls before a wait gives up (0: the default bound)
+    // The payload is already in the neighbours' mailboxes (the kernels that produced the rows
+    // stored it there): publish it, wait for the neighbours' rows, copy them in.  Parts whose
+    // halo pointers are null are waited for but not copied.
+    bool pull_only = false;
 };
 cudaError_t launch_halo_exchange(const HaloArgs& h, int sm_count, cudaStream_t s);
 

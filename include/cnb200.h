@@ -237,6 +237,7 @@ typedef struct cn_stats {
     int64_t deep_halo_sweeps;  /* stencil sweeps that also updated halo rows (see option "halo") */
     int64_t inlined_producers; /* whole-array assignments folded into the stencil kernel behind them */
     int64_t row_fetches;       /* operands of strided groups whose rows were fetched from other ranks */
+    int64_t halo_pushes;       /* outputs whose edge rows the producing kernel stored into the neighbours' mailboxes */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
@@ -262,6 +263,11 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
  * writing the array and reading it back: 1 the assigned values are recomputed at every stencil
  * point, 2 (default) they are computed tile by tile, halo ring included, into shared memory
  * where that form fits (2-D float64), recomputed otherwise; 0 two kernels),
+ * "push_halo" 0/1 (default 0, with "p2p": a kernel that rewrites an array whose halo a stencil
+ * has asked for before stores the slab's edge rows into the neighbours' mailboxes itself; a small
+ * kernel publishes them, waits for the neighbours' rows and copies those in when the stencil
+ * asks.  Measured slower than the stand-alone exchange kernel -- the peer stores and their
+ * registers cost the sweep more than the exchange launch they save -- so it is off),
  * "stencil_shfl" 0/1 (default 0, measured slower: cache-served stencil kernels take the
  * neighbours along the last dimension from neighbour lanes by warp shuffle). */
 int cn_set_option(cn_context* ctx, const char* key, int64_t value);

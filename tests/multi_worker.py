@@ -123,6 +123,7 @@ def main():
     result["overlapped_sweeps"] = np.array(st["overlapped_sweeps"])
     result["deep_halo_sweeps"] = np.array(st["deep_halo_sweeps"])
     result["row_fetches"] = np.array(st["row_fetches"])
+    result["halo_pushes"] = np.array(st["halo_pushes"])
     result["inlined_producers"] = np.array(st["inlined_producers"])
     np.savez(os.path.join(outdir, f"{case}_rank{rank}.npz"), **result)
     itf.close()

@@ -19,9 +19,9 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-def _run_ranks(tmp_path, case, nranks, p2p, overlap=0, halo=1):
+def _run_ranks(tmp_path, case, nranks, p2p, overlap=0, halo=1, push=0):
     idfile = str(tmp_path / "nccl_id")
-    env = dict(os.environ, CN_P2P=str(p2p), CN_OVERLAP_HALO=str(overlap), CN_HALO=str(halo))
+    env = dict(os.environ, CN_P2P=str(p2p), CN_OVERLAP_HALO=str(overlap), CN_HALO=str(halo), CN_PUSH_HALO=str(push))
     procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "multi_worker.py"), str(r), str(nranks),
                                idfile, str(tmp_path), case], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                               text=True, env=env) for r in range(nranks)]
@@ -108,6 +108,19 @@ def test_multi_gpu_cg_direction_update_inlined(tmp_path, nranks):
     _check("cg", results, 1)
     for d in results:
         assert int(d["inlined_producers"]) == 9
+
+
+@pytest.mark.parametrize("case,halo", [("jacobi2d", 1), ("jacobi3d", 1), ("cg_rotated", 1), ("jacobi2d_long", 4)])
+def test_multi_gpu_edge_rows_pushed_by_their_producers(tmp_path, case, halo):
+    """Option push_halo: after the first exchange the kernels that rewrite an array store its
+    edge rows into the neighbours' mailboxes themselves; a small kernel publishes them, waits
+    for the neighbours' and copies those in.  Same results, bit for bit."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    results = _run_ranks(tmp_path, case, 2, 1, halo=halo, push=1)
+    _check("cg" if case == "cg_rotated" else case.replace("_long", ""), results, 1)
+    for d in results:
+        assert int(d["halo_pushes"]) > 0
 
 
 @pytest.mark.parametrize("case", ["jacobi2d", "jacobi3d", "cg", "chain"])
