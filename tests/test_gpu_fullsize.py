@@ -169,6 +169,18 @@ def test_config4_matvec_properties(interface, oracle_mod):
     r = _run_gpu_only(interface, full)
     scale = np.max(np.abs(r["Axy"]))
     assert np.max(np.abs(r["Axy"] - (r["Ax"] + r["Ay"]))) <= 1e-12 * scale * 10
+    # closed form at the configured size: 256 rows of the seeded matrix are regenerated on the
+    # host (element (i, j) is value number i * N + j of the seeded generator) and multiplied by
+    # the regenerated x; a kernel that dropped or misplaced columns would not survive this
+    xh = oracle_mod.randu((N,), 1, -1.0, 1.0)
+    rows = np.unique(np.concatenate([[0, 1, N - 2, N - 1, N // 2 - 1, N // 2],
+                                     np.random.default_rng(5).integers(0, N, 250)]))
+    worst = 0.0
+    for i in rows:
+        a_row = oracle_mod.randu((N,), 0x5EED + 4, -1.0 / 256, 1.0 / 256, offset=int(i) * N)
+        want_i = oracle_mod.dot(a_row, xh, tile=4096)
+        worst = max(worst, abs(r["Ax"][i] - want_i))
+    assert worst <= RTOL * np.max(np.abs(r["Ax"])), worst
 
 
 def test_kernel_abi_compile_and_launch(interface):
