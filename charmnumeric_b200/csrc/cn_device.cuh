@@ -13,7 +13,9 @@
 #define CN_MAX_SC 16
 #define CN_MAX_RED 4
 #define CN_MAX_SOUT 4
-#define CN_BLOCK 256
+#ifndef CN_BLOCK
+#define CN_BLOCK 256  // threads per block; a generated kernel may be compiled for another size
+#endif
 #define CN_MAX_PEERS 8
 #define CN_PEER_HALO_SLOT (16u << 20)  // bytes per (bank, direction) halo payload slot
 

@@ -35,6 +35,13 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
             if (r.opcode == OP_EXP || r.opcode == OP_TANH || r.opcode == OP_SQRT || r.opcode == OP_DIV) ++heavy;
         if (heavy >= 2) tile.r = 4;
         heavy_flat = heavy >= 2;
+        // one block of 1024 threads per SM: measured 6 % faster on the 2^28 chain than four
+        // blocks of 256 (0.93 against 0.99 ms on a stand-alone copy of the kernel)
+        if (heavy_flat) tile.block = 1024;
+        if (const char* e = getenv("CN_FLAT_BLOCK")) {
+            const int v = atoi(e);
+            if (heavy_flat && (v == 128 || v == 256 || v == 512 || v == 1024)) tile.block = v;
+        }
     }
     if (g.staged) {
         // a staged tile is one TMA box: at most 256 elements per side
@@ -45,7 +52,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         // computed tiles carry a halo ring of redundant work: 128 x 32 points keep it below 10 %
         if (!g.producer.empty() && !staged_tile_set_) tile.r = 8;
         if (tile.tx > 64) tile.tx = 64;
-        while ((CN_BLOCK / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
+        while ((tile.block / tile.tx) * tile.r + 2 * g.hy > 256) tile.r /= 2;
     }
     if (g.cls == GroupIR::SHIFTED && !g.flat && g.ndims >= 2) {
         // specialise on the element strides of the (common) array shape
@@ -65,7 +72,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     // 2^28 chain: 1.18 -> 1.0 ms)
     tile.prefetch = !g.flat ? 0 : (flat_prefetch_ >= 0 ? flat_prefetch_ : (heavy_flat ? 2 : 0));
     if (g.staged && g.ndims == 3) tile.ns = staged_ns_ ? staged_ns_ : (g.hz == 1 ? 4 : 0);
-    std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "|S" +
+    std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "/" + std::to_string(tile.block) + "|S" +
                       std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
                       "|mb" + std::to_string(tile.minb) + "|fu" + std::to_string(tile.fill_u) +
                       "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "") + (tile.push ? "|push" : "");
@@ -98,7 +105,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     }
     if (g.staged) {
         const int ns = tile.ns ? tile.ns : (g.ndims == 3 ? 2 * g.hz + 3 : 3);
-        const size_t sw = (size_t)tile.tx * 2 + 4, sh = (size_t)(CN_BLOCK / tile.tx) * tile.r + 2 * g.hy;
+        const size_t sw = (size_t)tile.tx * 2 + 4, sh = (size_t)(tile.block / tile.tx) * tile.r + 2 * g.hy;
         const size_t slot = (sh * sw + 15) / 16 * 16;
         k.smem_bytes = ns * slot * sizeof(double) + ns * sizeof(unsigned long long);
         if (!g.producer.empty()) k.smem_bytes = slot * sizeof(double) + sizeof(unsigned long long);
@@ -108,7 +115,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
             return rc;
     }
     int occ = 0;
-    if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, CN_BLOCK, k.smem_bytes) == CUDA_SUCCESS && occ > 0)
+    if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, tile.block, k.smem_bytes) == CUDA_SUCCESS && occ > 0)
         k.blocks_per_sm = occ;
     if (g.staged && g.ndims == 3) {
         // measured on the 1024^3 sweep: four marching blocks per SM saturate HBM; a fifth only
@@ -215,7 +222,7 @@ int Context::encode_tensor_map(const Array& x, const CompiledGroup& k, const Gro
     cuuint32_t estr[3] = {1, 1, 1};
     const cuuint64_t rows0 = (cuuint64_t)(x.local_rows() + 2 * x.halo);
     const cuuint32_t sw = (cuuint32_t)k.tile.tx * 2 + 4;
-    const cuuint32_t sh = (cuuint32_t)(CN_BLOCK / k.tile.tx) * k.tile.r + 2 * g.hy;
+    const cuuint32_t sh = (cuuint32_t)(k.tile.block / k.tile.tx) * k.tile.r + 2 * g.hy;
     if (nd == 2) {
         dims[0] = (cuuint64_t)x.shape[1];
         dims[1] = rows0;
@@ -489,7 +496,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         a.hi[0] = n;
         a.rlo[0] = 0;
         a.rhi[0] = n;
-        int64_t per = (int64_t)k->tile.r * CN_BLOCK * V;
+        int64_t per = (int64_t)k->tile.r * k->tile.block * V;
         ntiles = (n + per - 1) / per;
     } else {
         for (int d = 0; d < nd; ++d) {
@@ -505,11 +512,11 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
             const int L = nd - 1;
             int64_t xbase = V == 2 ? (lo[L] & ~1LL) : lo[L];
             if (nd == 1) {
-                int64_t per = (int64_t)k->tile.r * CN_BLOCK * V;
+                int64_t per = (int64_t)k->tile.r * k->tile.block * V;
                 ntiles = (hi[0] - xbase + per - 1) / per;
             } else {
                 int64_t ntx = (hi[L] - xbase + (int64_t)k->tile.tx * V - 1) / ((int64_t)k->tile.tx * V);
-                int64_t rows_per = (int64_t)(CN_BLOCK / k->tile.tx) * k->tile.r;
+                int64_t rows_per = (int64_t)(k->tile.block / k->tile.tx) * k->tile.r;
                 int64_t nty = (hi[nd - 2] - lo[nd - 2] + rows_per - 1) / rows_per;
                 int64_t nz = nd == 3 ? hi[0] - lo[0] : 1;
                 a.ntx = ntx;
@@ -634,7 +641,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
                     int64_t bt = 0;
                     bool be = false;
                     if ((rc = plan(blo, bhi, b, &bgrid, &bt, &be))) return rc;
-                    if (bt > 0 && (rc = launch(k, b, bgrid, CN_BLOCK, row_bytes * (double)(bhi[0] - blo[0]),
+                    if (bt > 0 && (rc = launch(k, b, bgrid, k->tile.block, row_bytes * (double)(bhi[0] - blo[0]),
                                                part == 2 ? stream_ : stream2_)))
                         return rc;
                 }
@@ -650,7 +657,7 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
             if (overlap)
                 for (Array* x : stale)
                     if ((rc = exchange_halo(x, stream_))) return rc;
-            if ((rc = launch(k, a, grid, CN_BLOCK, bytes))) return rc;
+            if ((rc = launch(k, a, grid, k->tile.block, bytes))) return rc;
         }
     } else if (overlap) {
         for (Array* x : stale)
@@ -943,7 +950,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
     for (int d = 0; d < 3; ++d) a.ext[d] = d < nd ? ext[d] : 1;
     int64_t total = 1;
     for (int d = 0; d < nd; ++d) total *= ext[d];
-    int grid = (int)std::min<int64_t>(std::max<int64_t>((total + CN_BLOCK - 1) / CN_BLOCK, 1), (int64_t)sm_count_ * k->blocks_per_sm);
+    int grid = (int)std::min<int64_t>(std::max<int64_t>((total + k->tile.block - 1) / k->tile.block, 1), (int64_t)sm_count_ * k->blocks_per_sm);
     std::vector<Array*> results;
     if ((rc = bind_reductions(g, &a, grid, &results))) return rc;
     for (size_t q = 0; q < results.size(); ++q) {
@@ -951,7 +958,7 @@ int Context::run_strided(const GroupIR& g, CompiledGroup* k) {
         a.red[q] = results[q]->buf.data;
     }
     if (total > 0 || !g.reds.empty() || !g.souts.empty())
-        if ((rc = launch(k, a, grid, CN_BLOCK,
+        if ((rc = launch(k, a, grid, k->tile.block,
                          (double)total * (double)(g.leaves.size() + g.outs.size()) * dtype_size(g.dtype))))
             return rc;
     for (auto& p : copy_back) {
@@ -1655,8 +1662,8 @@ int Context::launch_group(uint64_t handle, int n_in, void* const* in_ptrs, const
         total *= a.ext[d];
     }
     if (total <= 0) return CN_OK;
-    int grid = (int)std::min<int64_t>((total + CN_BLOCK - 1) / CN_BLOCK, (int64_t)sm_count_ * 8);
-    return launch(k, a, grid, CN_BLOCK, (double)total * (n_in + n_out) * dtype_size(g.dtype));
+    int grid = (int)std::min<int64_t>((total + k->tile.block - 1) / k->tile.block, (int64_t)sm_count_ * 8);
+    return launch(k, a, grid, k->tile.block, (double)total * (n_in + n_out) * dtype_size(g.dtype));
 }
 
 }  // namespace cn

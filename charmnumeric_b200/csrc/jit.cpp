@@ -86,6 +86,7 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
     std::string d_s0 = "-DCN_S0=" + std::to_string(tile.s0) + "LL";
     std::string d_s1 = "-DCN_S1=" + std::to_string(tile.s1) + "LL";
     std::string d_ns = "-DCN_NS_OVERRIDE=" + std::to_string(tile.ns);
+    std::string d_bl = "-DCN_BLOCK=" + std::to_string(tile.block > 0 ? tile.block : 256);
     std::string d_mb = "-DCN_MINB=" + std::to_string(tile.minb > 0 ? tile.minb : 1);
     std::string d_fu = "-DCN_FILL_U=" + std::to_string(tile.fill_u > 0 ? tile.fill_u : 1);
     std::string d_pf = "-DCN_PREFETCH=" + std::to_string(tile.prefetch);
@@ -95,6 +96,7 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
                           "--prec-sqrt=true",           "--std=c++17",     "-lineinfo",
                           d_tx.c_str(),                 d_r.c_str(),       d_s0.c_str(),
                           d_s1.c_str(),                 d_ns.c_str(),
+                          d_bl.c_str(),
                           d_mb.c_str(),                 d_fu.c_str(),
                           d_pf.c_str(),                 tile.shfl ? "-DCN_SHFL=1" : "-DCN_SHFL=0",
                           tile.push ? "-DCN_PUSH=1" : "-DCN_PUSH=0",

@@ -14,6 +14,7 @@
 namespace cn {
 
 struct TileConfig {
+    int block = 256;  // threads per block
     int tx = 256;  // threads along the last dimension
     int r = 2;     // consecutive rows per thread
     // element strides of the arrays a stencil kernel is specialised for (0: read at run time);
