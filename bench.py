@@ -61,20 +61,26 @@ def measured_peak():
 
 
 def dram_traffic(kernel):
-    """DRAM bytes per launch of a kernel, from the committed ncu capture of that kernel
-    (profiles/dram_traffic.json: measured dram read+write bytes per algorithmic byte on a
-    reduced-size case; traffic of these streaming kernels grows in proportion to the points
-    processed).  None when no capture covers the kernel."""
+    """(DRAM bytes per launch, where the figure comes from) of a kernel, from the committed ncu
+    capture of that kernel (profiles/dram_traffic.json: measured dram read+write bytes per
+    algorithmic byte on a reduced-size case; traffic of these streaming kernels grows in
+    proportion to the points processed).  An entry names the code digest of the kernel it was
+    captured from (the `#xxxxxxxx` the library puts at the end of a kernel's label: source,
+    device header and tile configuration); a capture of another version of the kernel is not
+    used.  (None, reason) when no capture covers the running kernel."""
     try:
         table = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
     except Exception:
-        return None
+        return None, "profiles/dram_traffic.json not readable"
     label = kernel["kernel"]
     for entry in table.get("kernels", []):
         if entry["match"] in label:
+            if entry.get("code") and entry["code"] not in label:
+                return None, (f"{entry['source']} was captured from another version of this kernel "
+                              f"({entry['code']})")
             algorithmic = kernel["gbs"] * 1e9 * kernel["ms_per_launch"] * 1e-3
-            return entry["dram_bytes_per_algorithmic_byte"] * algorithmic
-    return None
+            return entry["dram_bytes_per_algorithmic_byte"] * algorithmic, "profiles/" + entry["source"]
+    return None, "no capture of this kernel"
 
 
 class ClockSampler:
@@ -466,8 +472,10 @@ def measure(name, args, itf, dist, rank, world, local_rank, primary):
                                 "ms_per_launch": r["ms"] / max(1, r["launches"]),
                                 "share": r["ms"] / total_ms, "gbs": gbs})
             top = kernels[0]
+            traffic, traffic_from = dram_traffic(top)
             roofline = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
-                        "frac": top["gbs"] / peak, "traffic": dram_traffic(top), "kernel": top["kernel"],
+                        "frac": top["gbs"] / peak, "traffic": traffic, "traffic_from": traffic_from,
+                        "kernel": top["kernel"],
                         "peak_kind": peak_kind, "nominal_frac": top["gbs"] / 8000.0}
         # weak scaling: every GPU iterates its own slab of the (N times larger) global grid, so the
         # whole-job figure is GPUs x iterations/s; strong scaling: one fixed problem, steps/s

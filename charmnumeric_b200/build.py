@@ -26,13 +26,17 @@ def _embed():
     """Write embedded_headers.cpp holding the texts NVRTC needs."""
     dev = (CSRC / "cn_device.cuh").read_text()
     tab = (CSRC / "cn_exp_table.inc").read_text()
+    aot = hashlib.sha256((CSRC / "kernels.cu").read_bytes() + (CSRC / "kernels.hpp").read_bytes()).hexdigest()[:8]
     def lit(text):
         # split into chunks: one raw string literal must stay below compiler limits
         parts = [text[i:i + 8000] for i in range(0, len(text), 8000)]
         return "\n".join('R"CNB200(' + p + ')CNB200"' for p in parts)
     body = ('#include "jit.hpp"\nnamespace cn {\n'
             "const char* const kDeviceHeaderText =\n" + lit(dev) + ";\n"
-            "const char* const kExpTableText =\n" + lit(tab) + ";\n}\n")
+            "const char* const kExpTableText =\n" + lit(tab) + ";\n"
+            # the kernels built ahead of time (matvec, dot, halo copies) are identified in
+            # profile labels by a digest of their source
+            'const char* const kAotSourceDigest = "' + aot + '";\n}\n')
     path = BUILD / "embedded_headers.cpp"
     if not path.exists() or path.read_text() != body:
         path.write_text(body)

@@ -114,6 +114,11 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
                                                     (int)k.smem_bytes), "cuFuncSetAttribute")))
             return rc;
     }
+    {
+        char tag[16];
+        snprintf(tag, sizeof(tag), " #%08x", code_digest(k.source, tile));
+        k.label += tag;
+    }
     int occ = 0;
     if (drv_.OccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.func, tile.block, k.smem_bytes) == CUDA_SUCCESS && occ > 0)
         k.blocks_per_sm = occ;
@@ -1039,7 +1044,7 @@ int Context::execute_reduce(const AstNode& r) {
     if ((rc = create_array(r.result_name, 1, one, dtype, false, &res))) return rc;
     int grid = dot_grid_size(n, sm_count_);
     if (grid > max_grid_) grid = max_grid_;
-    prof_start(py ? "dot" : "sum", (double)n * (py ? 2 : 1) * dtype_size(dtype));
+    prof_start(std::string(py ? "dot #" : "sum #") + kAotSourceDigest, (double)n * (py ? 2 : 1) * dtype_size(dtype));
     rc = cuda_fail(launch_dot(px, py, n, dtype, partials_, counter_, res->buf.data, grid, stream_), "dot");
     prof_stop();
     if (rc) return rc;
@@ -1078,7 +1083,7 @@ int Context::execute_matmul(const AstNode& r) {
     if (nranks_ == 1) {
         const char* pa = A->buf.data + (ra.start[0] * A->shape[1] + ra.start[1]) * esz;
         const char* px = x->buf.data + rx.start[0] * esz;
-        prof_start("matvec", ((double)rows * cols + rows + cols) * esz);
+        prof_start(std::string("matvec #") + kAotSourceDigest, ((double)rows * cols + rows + cols) * esz);
         rc = cuda_fail(launch_matvec(pa, A->shape[1], px, y->buf.data, rows, cols, dtype, stream_), "matvec");
         prof_stop();
         if (rc) return rc;
@@ -1116,7 +1121,7 @@ int Context::execute_matmul(const AstNode& r) {
     const int64_t my_rows = y->local_rows();
     const char* pa = (moved ? moved : A->buf.data) + ((ra.start[0] + y->row_begin - base_row) * A->shape[1] + ra.start[1]) * esz;
     const char* px = (const char*)scratch_ + rx.start[0] * esz;
-    prof_start("matvec", ((double)my_rows * cols + my_rows + cols) * esz);
+    prof_start(std::string("matvec #") + kAotSourceDigest, ((double)my_rows * cols + my_rows + cols) * esz);
     rc = cuda_fail(launch_matvec(pa, A->shape[1], px, y->buf.data, my_rows, cols, dtype, stream_), "matvec");
     prof_stop();
     for (void* t : fetched) cudaFreeAsync(t, stream_);

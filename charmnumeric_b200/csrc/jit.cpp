@@ -3,6 +3,8 @@
 // on the loader path.
 #include "jit.hpp"
 
+#include <cstring>
+
 #include <dlfcn.h>
 
 #include <cstdlib>
@@ -65,6 +67,23 @@ NvrtcApi* load_nvrtc() {
 }
 
 }  // namespace
+
+uint32_t code_digest(const std::string& source, const TileConfig& tile) {
+    uint32_t h = 2166136261u;  // FNV-1a
+    auto mix = [&](const char* p, size_t n) {
+        for (size_t i = 0; i < n; ++i) {
+            h ^= (unsigned char)p[i];
+            h *= 16777619u;
+        }
+    };
+    mix(source.data(), source.size());
+    mix(kDeviceHeaderText, strlen(kDeviceHeaderText));
+    char cfg[160];
+    const int n = snprintf(cfg, sizeof(cfg), "tx%d r%d b%d ns%d pf%d sh%d push%d mb%d fu%d", tile.tx, tile.r, tile.block,
+                           tile.ns, tile.prefetch, (int)tile.shfl, (int)tile.push, tile.minb, tile.fill_u);
+    mix(cfg, (size_t)n);
+    return h;
+}
 
 int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector<char>* cubin,
                   std::string* log) {

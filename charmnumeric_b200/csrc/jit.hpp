@@ -6,6 +6,7 @@
 // (src/jit.cpp:463-540), which emit PTX for sm_70 and load it with the driver API.
 #pragma once
 #include <map>
+#include <cstdint>
 #include <string>
 #include <vector>
 
@@ -42,8 +43,16 @@ struct TileConfig {
 int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector<char>* cubin,
                   std::string* log);
 
+// Digest of everything that decides a generated kernel's machine code apart from the array
+// strides it is specialised on: the generated source, the device header and the tile
+// configuration.  Profile labels carry it, so that a stored measurement of a kernel can be
+// told from a measurement of an earlier version of that kernel.
+uint32_t code_digest(const std::string& source, const TileConfig& tile);
+
 // Texts of the headers every generated kernel includes (embedded at build time).
 extern const char* const kDeviceHeaderText;
 extern const char* const kExpTableText;
+// Digest of the sources of the kernels built ahead of time (matvec, dot / sum, halo copies).
+extern const char* const kAotSourceDigest;
 
 }  // namespace cn
