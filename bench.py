@@ -409,7 +409,10 @@ def measure(name, args, itf, dist, rank, world, local_rank, primary):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()  # nvidia-smi needs a few hundred ms before its first sample
-    wl = WORKLOADS[name](itf, nranks=world, scale=args.scale)
+    extra = {}
+    if args.res_every >= 0 and name in ("jacobi2d", "jacobi3d"):
+        extra["res_every"] = args.res_every  # diagnostic: how much of a step the residual costs
+    wl = WORKLOADS[name](itf, nranks=world, scale=args.scale, **extra)
     K, W = max(1, args.steps), max(3, args.warmup)
 
     # every distinct step blob once, so that no run-time compilation lands in a timed region
@@ -487,7 +490,7 @@ def measure(name, args, itf, dist, rank, world, local_rank, primary):
             "bursts": {"count": len(times), "steps_each": K, "median_ms": ms, "min_ms": min(times),
                        "max_ms": max(times), "value_best": agg * K / (min(times) * 1e-3),
                        "value_worst": agg * K / (max(times) * 1e-3)},
-            "config": config_for(name, world, args.scale, halo),
+            "config": dict(config_for(name, world, args.scale, halo), **({"res_every": extra["res_every"]} if extra else {})),
             "roofline": roofline,
             "step_hbm": {"algorithmic_bytes_per_step_per_gpu": wl.bytes_per_step / world,
                          "gbs_per_gpu": step_gbs, "frac_of_" + peak_kind: step_gbs / peak,
@@ -589,6 +592,8 @@ def main():
                     help="five timed bursts only (profiling runs); the clock sampler may then see too little load")
     ap.add_argument("--no-check", action="store_true", help="skip the untimed parity check against the oracle")
     ap.add_argument("--halo", type=int, default=0, help="halo rows per side for N > 1 (0: per-workload default)")
+    ap.add_argument("--res-every", type=int, default=-1,
+                    help="Jacobi workloads: residual every n-th sweep (0: never; default: the configured 10)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -373,6 +373,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
     } else if (k == "fuse_producers") {
         if (value < 0 || value > 2) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_fuse_producers((int)value);
+    } else if (k == "dependent_launch") {
+        ctx->impl.set_dependent_launch(value != 0);
     } else if (k == "stencil_shfl") {
         ctx->impl.set_stencil_shfl(value != 0);
     } else if (k == "plan_cache") {

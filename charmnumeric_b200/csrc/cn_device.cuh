@@ -240,6 +240,22 @@ __device__ __forceinline__ A cn_sum_partials(const A* partials, A* smem) {
 #define CN_PEER_WAIT_LIMIT 4000000u
 #endif
 
+// First statement of every generated kernel.  When the kernel was launched with programmatic
+// stream serialisation, its launch is released as soon as the blocks of the previous kernel of
+// the stream have exited (or, with CN_TRIGGER, as soon as they have all started) instead of
+// after that kernel has drained; `wait` returns once the previous kernel has completed and
+// its writes are visible.  Nothing before this point touches global memory.  Without the
+// launch attribute both instructions do nothing.
+#ifndef CN_TRIGGER
+#define CN_TRIGGER 0
+#endif
+__device__ __forceinline__ void cn_stream_dependency() {
+#if CN_TRIGGER
+    asm volatile("griddepcontrol.launch_dependents;");
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ void cn_st_release_sys(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }

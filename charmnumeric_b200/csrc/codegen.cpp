@@ -103,6 +103,7 @@ struct Gen {
         if (g.vec == 2) o << "typedef " << (g.dtype == DT_I64 ? "longlong2" : "double2") << " T2;\n";
         o << "extern \"C\" __global__ void __launch_bounds__(CN_BLOCK, CN_MINB) " << g.entry_name() << "("
              "const __grid_constant__ CnGroupArgs a) {\n";
+        o << "  cn_stream_dependency();\n";
         for (size_t i = 0; i < g.scalars.size(); ++i)
             o << "  const T c" << i << " = (T)a.sc[" << i << "];\n";
         for (size_t i = 0; i < g.bcast_names.size(); ++i)

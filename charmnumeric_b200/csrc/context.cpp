@@ -41,6 +41,7 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_PUSH_HALO")) push_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_FUSE_PRODUCERS")) fuse_producers_ = std::max(0, std::min(2, atoi(f)));
     if (const char* f = getenv("CN_STENCIL_SHFL")) stencil_shfl_ = atoi(f) != 0;
+    if (const char* f = getenv("CN_DEPENDENT_LAUNCH")) dependent_launch_ = atoi(f) != 0;
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
     if (const char* f = getenv("CN_OVERLAP_HALO")) overlap_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_DEEP_HALO")) deep_halo_ = atoi(f) != 0;
@@ -164,6 +165,7 @@ int Context::init() {
     CN_DRV(ModuleGetFunction, "cuModuleGetFunction")
     CN_DRV(ModuleUnload, "cuModuleUnload")
     CN_DRV(LaunchKernel, "cuLaunchKernel")
+    CN_DRV(LaunchKernelEx, "cuLaunchKernelEx")
     CN_DRV(GetErrorString, "cuGetErrorString")
     CN_DRV(OccupancyMaxActiveBlocksPerMultiprocessor, "cuOccupancyMaxActiveBlocksPerMultiprocessor")
     CN_DRV(FuncSetAttribute, "cuFuncSetAttribute")

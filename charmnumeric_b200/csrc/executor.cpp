@@ -64,6 +64,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
         if (const char* e = getenv("CN_PRODUCER_FILL_U")) tile.fill_u = std::max(1, std::min(9, atoi(e)));
     }
     tile.drop_copies = g.staged && debug_drop_copies_;
+    if (const char* e = getenv("CN_LAUNCH_TRIGGER")) tile.trigger = atoi(e) != 0;
     tile.shfl = stencil_shfl_ && g.cls == GroupIR::SHIFTED && !g.flat && !g.staged;
     tile.push = push_halo_ && nranks_ > 1 && peer_.ready && g.cls == GroupIR::SHIFTED && !overlap_halo_;
     // heavy flat groups issue the loads of all their rows before the arithmetic: between the
@@ -75,7 +76,8 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     std::string key = g.key() + "|T" + std::to_string(tile.tx) + "," + std::to_string(tile.r) + "/" + std::to_string(tile.block) + "|S" +
                       std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
                       "|mb" + std::to_string(tile.minb) + "|fu" + std::to_string(tile.fill_u) +
-                      "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "") + (tile.push ? "|push" : "");
+                      "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "") + (tile.push ? "|push" : "") +
+                      (tile.trigger ? "|trig" : "");
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -193,10 +195,28 @@ int Context::launch(CompiledGroup* k, const CnGroupArgs& a, int grid, int block,
     if (!st) st = stream_;
     void* params[] = {(void*)&a};
     prof_start(k->label, bytes, st);
-    int rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1,
-                                           (unsigned)k->smem_bytes,
-                                           (CUstream)st, params, nullptr),
+    int rc;
+    if (dependent_launch_) {
+        CUlaunchAttribute attr;
+        memset(&attr, 0, sizeof(attr));
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+        CUlaunchConfig cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDimX = (unsigned)grid;
+        cfg.gridDimY = cfg.gridDimZ = 1;
+        cfg.blockDimX = (unsigned)block;
+        cfg.blockDimY = cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = (unsigned)k->smem_bytes;
+        cfg.hStream = (CUstream)st;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        rc = driver_fail(drv_.LaunchKernelEx(&cfg, k->func, params, nullptr), "cuLaunchKernelEx");
+    } else {
+        rc = driver_fail(drv_.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1,
+                                           (unsigned)k->smem_bytes, (CUstream)st, params, nullptr),
                          "cuLaunchKernel");
+    }
     prof_stop();
     if (rc) return rc;
     stats_.kernel_launches++;

@@ -79,8 +79,8 @@ uint32_t code_digest(const std::string& source, const TileConfig& tile) {
     mix(source.data(), source.size());
     mix(kDeviceHeaderText, strlen(kDeviceHeaderText));
     char cfg[160];
-    const int n = snprintf(cfg, sizeof(cfg), "tx%d r%d b%d ns%d pf%d sh%d push%d mb%d fu%d", tile.tx, tile.r, tile.block,
-                           tile.ns, tile.prefetch, (int)tile.shfl, (int)tile.push, tile.minb, tile.fill_u);
+    const int n = snprintf(cfg, sizeof(cfg), "tx%d r%d b%d ns%d pf%d sh%d push%d mb%d fu%d tr%d", tile.tx, tile.r, tile.block,
+                           tile.ns, tile.prefetch, (int)tile.shfl, (int)tile.push, tile.minb, tile.fill_u, (int)tile.trigger);
     mix(cfg, (size_t)n);
     return h;
 }
@@ -119,6 +119,7 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
                           d_mb.c_str(),                 d_fu.c_str(),
                           d_pf.c_str(),                 tile.shfl ? "-DCN_SHFL=1" : "-DCN_SHFL=0",
                           tile.push ? "-DCN_PUSH=1" : "-DCN_PUSH=0",
+                          tile.trigger ? "-DCN_TRIGGER=1" : "-DCN_TRIGGER=0",
                           tile.drop_copies ? "-DCN_DEBUG_DROP_COPIES=1" : "-DCN_DEBUG_DROP_COPIES=0",
                           tile.drop_copies ? "-DCN_WAIT_LIMIT=2000u" : "-DCN_WAIT_LIMIT=2000000u"};
     rc = api->CompileProgram(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);

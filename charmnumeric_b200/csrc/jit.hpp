@@ -34,6 +34,11 @@ struct TileConfig {
     // kernels of a multi-rank context can store their slab's edge rows into the neighbours'
     // mailboxes themselves (the launch arguments say when)
     bool push = false;
+    // the kernel releases the next kernel of the stream as soon as all its own blocks have
+    // started (instead of when they have exited).  Measured harmful: the next kernel's blocks
+    // take every free slot of the SMs and wait there (CG 8192^2 888 -> 1 001 us per iteration,
+    // Jacobi3D 1024^3 3.08 -> 3.68 ms), so it is off
+    bool trigger = false;
     int minb = 1;    // resident blocks per SM the compiler has to leave room for (register cap)
     int fill_u = 3;  // staged producers: points per thread whose loads are issued together
 };
