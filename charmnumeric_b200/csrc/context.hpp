@@ -258,6 +258,10 @@ private:
     // kernel to drain (each kernel waits for its predecessor's completion before it touches
     // memory).  Measured: Jacobi2D 2048^2 14.2 -> 12.1 us per sweep, CG 8192^2 888 -> 882 us
     bool dependent_launch_ = true;
+    // resident blocks per SM the cache-served stencil kernels are compiled for (a register cap);
+    // measured on the 5-point sweep, 1 (no cap) / 6 / 8: 12.2 / 10.6 / 10.7 us at 2048^2,
+    // 195 / 178 us at 8192^2, 875 / 750 us at 16384^2; larger groups spill at 7 and 8
+    int shifted_minb_ = 6;
     bool stencil_shfl_ = false;       // cache-served stencil kernels take x-neighbours by warp shuffle
     bool plan_cache_ = true;
     std::unordered_map<uint64_t, Plan> plans_;  // keyed by a hash of the blob bytes

@@ -77,19 +77,38 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
                       std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
                       "|mb" + std::to_string(tile.minb) + "|fu" + std::to_string(tile.fill_u) +
                       "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "") + (tile.push ? "|push" : "") +
-                      (tile.trigger ? "|trig" : "");
+                      (tile.trigger ? "|trig" : "") + "|sb" + std::to_string(shifted_minb_);
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
         return CN_OK;
     }
     CompiledGroup k;
-    k.tile = tile;
     int rc = generate_source(g, &k.source, &err_);
     if (rc) return rc;
     std::vector<char> cubin;
-    rc = nvrtc_compile(k.source, tile, &cubin, &k.log);
-    if (rc) return fail(rc, "group kernel failed to compile:\n" + k.log);
+    // Cache-served stencil kernels are bound by the latency of their loads: with the registers
+    // capped for six resident blocks per SM (30 instead of 44 registers for a 5-point sweep,
+    // which then runs eight blocks) more warps are in flight.  A group too large for the cap
+    // would spill, and is compiled again without it.
+    const bool cap_registers = g.cls == GroupIR::SHIFTED && !g.flat && !g.staged && tile.block == 256 &&
+                               tile.minb == 1 && shifted_minb_ > 1;
+    if (cap_registers) {
+        TileConfig tight = tile;
+        tight.minb = shifted_minb_;
+        std::string log;
+        if (nvrtc_compile(k.source, tight, &cubin, &log) == CN_OK && spill_bytes(log) == 0) {
+            tile = tight;
+            k.log = log;
+        } else {
+            cubin.clear();
+        }
+    }
+    k.tile = tile;
+    if (cubin.empty()) {
+        rc = nvrtc_compile(k.source, tile, &cubin, &k.log);
+        if (rc) return fail(rc, "group kernel failed to compile:\n" + k.log);
+    }
     stats_.compiles++;
     if ((rc = driver_fail(drv_.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData"))) return rc;
     rc = driver_fail(drv_.ModuleGetFunction(&k.func, k.module, g.entry_name().c_str()), "cuModuleGetFunction");

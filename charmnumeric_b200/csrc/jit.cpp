@@ -68,6 +68,20 @@ NvrtcApi* load_nvrtc() {
 
 }  // namespace
 
+long long spill_bytes(const std::string& log) {
+    long long total = 0;
+    for (const char* what : {" bytes spill stores", " bytes spill loads"}) {
+        size_t at = 0;
+        while ((at = log.find(what, at)) != std::string::npos) {
+            size_t b = at;
+            while (b > 0 && log[b - 1] >= '0' && log[b - 1] <= '9') --b;
+            if (b < at) total += atoll(log.substr(b, at - b).c_str());
+            at += 1;
+        }
+    }
+    return total;
+}
+
 uint32_t code_digest(const std::string& source, const TileConfig& tile) {
     uint32_t h = 2166136261u;  // FNV-1a
     auto mix = [&](const char* p, size_t n) {
@@ -111,7 +125,9 @@ int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector
     std::string d_pf = "-DCN_PREFETCH=" + std::to_string(tile.prefetch);
     // --fmad=false: a*b+c stays two roundings, as in the reference's arith.mulf/addf pairs
     // (src/jit.cpp:411-443); division and sqrt stay IEEE-rounded (the defaults, spelled out).
+    // --ptxas-options=-v: the log then states registers and spills of the kernel
     const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false",    "--prec-div=true",
+                          "--ptxas-options=-v",
                           "--prec-sqrt=true",           "--std=c++17",     "-lineinfo",
                           d_tx.c_str(),                 d_r.c_str(),       d_s0.c_str(),
                           d_s1.c_str(),                 d_ns.c_str(),

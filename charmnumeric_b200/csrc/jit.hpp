@@ -48,6 +48,9 @@ struct TileConfig {
 int nvrtc_compile(const std::string& source, const TileConfig& tile, std::vector<char>* cubin,
                   std::string* log);
 
+// Bytes of register spills the compiler reported in an NVRTC log (0 when it reported none).
+long long spill_bytes(const std::string& log);
+
 // Digest of everything that decides a generated kernel's machine code apart from the array
 // strides it is specialised on: the generated source, the device header and the tile
 // configuration.  Profile labels carry it, so that a stored measurement of a kernel can be
