@@ -43,6 +43,7 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_STENCIL_SHFL")) stencil_shfl_ = atoi(f) != 0;
     if (const char* f = getenv("CN_DEPENDENT_LAUNCH")) dependent_launch_ = atoi(f) != 0;
     if (const char* f = getenv("CN_STENCIL_BLOCKS")) shifted_minb_ = std::max(1, std::min(8, atoi(f)));
+    if (const char* f = getenv("CN_FLAT_BLOCKS")) flat_minb_ = std::max(1, std::min(8, atoi(f)));
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
     if (const char* f = getenv("CN_OVERLAP_HALO")) overlap_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_DEEP_HALO")) deep_halo_ = atoi(f) != 0;

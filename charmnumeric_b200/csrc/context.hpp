@@ -262,6 +262,9 @@ private:
     // measured on the 5-point sweep, 1 (no cap) / 6 / 8: 12.2 / 10.6 / 10.7 us at 2048^2,
     // 195 / 178 us at 8192^2, 875 / 750 us at 16384^2; larger groups spill at 7 and 8
     int shifted_minb_ = 6;
+    // the same cap for flat kernels (1: none).  Measured without effect: the CG update kernel
+    // at 40 registers / 6 blocks takes 522 us against 519 us at 48 / 5
+    int flat_minb_ = 1;
     bool stencil_shfl_ = false;       // cache-served stencil kernels take x-neighbours by warp shuffle
     bool plan_cache_ = true;
     std::unordered_map<uint64_t, Plan> plans_;  // keyed by a hash of the blob bytes

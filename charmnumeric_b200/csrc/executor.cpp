@@ -77,7 +77,7 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
                       std::to_string(tile.s0) + "," + std::to_string(tile.s1) + (tile.drop_copies ? "|drop" : "") + "|N" + std::to_string(tile.ns) +
                       "|mb" + std::to_string(tile.minb) + "|fu" + std::to_string(tile.fill_u) +
                       "|pf" + std::to_string(tile.prefetch) + (tile.shfl ? "|sh" : "") + (tile.push ? "|push" : "") +
-                      (tile.trigger ? "|trig" : "") + "|sb" + std::to_string(shifted_minb_);
+                      (tile.trigger ? "|trig" : "") + "|sb" + std::to_string(shifted_minb_) + "," + std::to_string(flat_minb_);
     auto it = kernels_.find(key);
     if (it != kernels_.end()) {
         *out = &it->second;
@@ -91,11 +91,12 @@ int Context::get_kernel(const GroupIR& g, CompiledGroup** out) {
     // capped for six resident blocks per SM (30 instead of 44 registers for a 5-point sweep,
     // which then runs eight blocks) more warps are in flight.  A group too large for the cap
     // would spill, and is compiled again without it.
-    const bool cap_registers = g.cls == GroupIR::SHIFTED && !g.flat && !g.staged && tile.block == 256 &&
-                               tile.minb == 1 && shifted_minb_ > 1;
+    const int cap_blocks = (g.cls == GroupIR::SHIFTED && !g.staged && tile.block == 256 && tile.minb == 1)
+                               ? (g.flat ? flat_minb_ : shifted_minb_) : 1;
+    const bool cap_registers = cap_blocks > 1;
     if (cap_registers) {
         TileConfig tight = tile;
-        tight.minb = shifted_minb_;
+        tight.minb = cap_blocks;
         std::string log;
         if (nvrtc_compile(k.source, tight, &cubin, &log) == CN_OK && spill_bytes(log) == 0) {
             tile = tight;
