@@ -24,7 +24,7 @@ class Stats(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
         "kernel_launches", "group_launches", "compiles", "halo_exchanges", "allreduces",
         "fused_reductions", "nodes", "bytes_h2d", "bytes_d2h", "plan_hits", "peer_exchanges", "overlapped_sweeps", "deep_halo_sweeps",
-        "inlined_producers", "row_fetches", "halo_pushes")]
+        "inlined_producers", "row_fetches", "halo_pushes", "scalar_tails")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -69,6 +69,8 @@ SIGNATURES = {
                                          C.c_char_p, C.c_int]),
     "cn_fuse_check": (C.c_int, [C.c_char_p, C.c_int64, C.c_char_p, C.c_int64, C.c_char_p, C.c_int64,
                                 C.POINTER(C.c_int), C.c_char_p, C.c_int]),
+    "cn_tail_check": (C.c_int, [C.c_char_p, C.c_int64, C.c_char_p, C.c_int64, C.POINTER(C.c_int),
+                                C.c_char_p, C.c_int]),
     "cn_region_intersect": (C.c_int, [_I64P, _I64P, _I64P]),
     "cn_region_map": (C.c_int, [_I64P, _I64P, _I64P, _I64P]),
     "cn_plan_row_transfers": (C.c_int, [_I64P, C.c_int64, _I64P, C.c_int64, C.c_int, _I64P, C.c_int64,

@@ -232,6 +232,20 @@ def fuse_check(node_a, node_b):
     return src.value.decode() if fused.value else None
 
 
+def tail_check(blob):
+    """Host-only: ``blob`` holds a group node, the REDUCE / SUM nodes its kernel takes in and a
+    node of size-1 arithmetic; returns the CUDA source of the single kernel when that last node
+    runs as the kernel's scalar tail, else None."""
+    lib = _lib.load()
+    src = C.create_string_buffer(1 << 18)
+    err = C.create_string_buffer(1 << 14)
+    fused = C.c_int(0)
+    status = lib.cn_tail_check(blob, len(blob), src, len(src), C.byref(fused), err, len(err))
+    if status != 0:
+        raise _lib.CnError(status, err.value.decode())
+    return src.value.decode() if fused.value else None
+
+
 def dag_check(blob):
     """Host-only: parse a DAG blob; returns (n_nodes, n_roots)."""
     lib = _lib.load()

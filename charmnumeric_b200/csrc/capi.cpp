@@ -261,6 +261,61 @@ int cn_fuse_check(const char* node_a, int64_t size_a, const char* node_b, int64_
     return cn::CN_OK;
 }
 
+int cn_tail_check(const char* dag_blob, int64_t size, char* source, int64_t cap, int* fused, char* err,
+                  int errcap) {
+    if (fused) *fused = 0;
+    cn::Dag dag;
+    std::string e;
+    int rc = cn::parse_dag(dag_blob, size, &dag, &e);
+    if (rc) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    if (dag.nodes.size() < 3) return cn::CN_ERR_INVALID_ARGUMENT;
+    std::vector<const cn::AstNode*> reds;
+    for (size_t i = 1; i + 1 < dag.nodes.size(); ++i) {
+        const cn::DagNode& n = dag.nodes[i];
+        if (n.roots.size() != 1 || (n.roots[0]->opcode != cn::OP_REDUCE && n.roots[0]->opcode != cn::OP_SUM))
+            return cn::CN_ERR_INVALID_ARGUMENT;
+        reds.push_back(n.roots[0].get());
+    }
+    cn::GroupIR g, t;
+    if ((rc = cn::lower_group(dag.nodes[0], reds, &g, &e))) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    if (g.cls != cn::GroupIR::SHIFTED || g.reds.empty()) return cn::CN_OK;
+    if (cn::lower_group(dag.nodes.back(), {}, &t, &e) != cn::CN_OK || t.cls != cn::GroupIR::SCALAR_ONLY ||
+        t.dtype != g.dtype || t.souts.empty()) {
+        copy_err(e, err, errcap);
+        return cn::CN_OK;
+    }
+    g.tail.push_back(t);
+    std::string src;
+    if ((rc = cn::generate_source(g, &src, &e))) {
+        copy_err(e, err, errcap);
+        return rc;
+    }
+    std::vector<char> cubin;
+    std::string log;
+    cn::TileConfig tile;
+    if (g.staged) {
+        tile.tx = 64;
+        tile.r = 4;
+    }
+    if ((rc = cn::nvrtc_compile(src, tile, &cubin, &log))) {
+        copy_err(log, err, errcap);
+        return rc;
+    }
+    if (source && cap > 0) {
+        size_t n = std::min<size_t>(src.size(), (size_t)cap - 1);
+        memcpy(source, src.data(), n);
+        source[n] = 0;
+    }
+    if (fused) *fused = 1;
+    return cn::CN_OK;
+}
+
 static cn::Lattice lat(const int64_t* r) { return cn::Lattice{r[0], r[1], r[2]}; }
 
 int cn_region_intersect(const int64_t a[3], const int64_t b[3], int64_t out[3]) {
@@ -341,6 +396,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out) {
     out->inlined_producers = s.inlined_producers;
     out->row_fetches = s.row_fetches;
     out->halo_pushes = s.halo_pushes;
+    out->scalar_tails = s.scalar_tails;
     return cn::CN_OK;
 }
 
@@ -373,6 +429,8 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
     } else if (k == "fuse_producers") {
         if (value < 0 || value > 2) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_fuse_producers((int)value);
+    } else if (k == "fuse_scalar_tail") {
+        ctx->impl.set_fuse_scalar_tail(value != 0);
     } else if (k == "dependent_launch") {
         ctx->impl.set_dependent_launch(value != 0);
     } else if (k == "stencil_shfl") {

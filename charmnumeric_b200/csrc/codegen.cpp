@@ -151,8 +151,39 @@ struct Gen {
         o << "    if (a.peer_n > 1) cn_peer_allreduce(a, tv, " << g.reds.size() << ", cn_sm);\n";
         for (size_t i = 0; i < g.reds.size(); ++i)
             o << "    if (threadIdx.x == 0) *(T*)a.red[" << i << "] = (T)tv[" << i << "];\n";
+        scalar_tail();
         o << "    if (threadIdx.x == 0) *a.counter = 0u;\n";
         o << "  }\n";
+    }
+
+    // The scalar group behind the reductions, evaluated by the thread that has just stored
+    // their results (it reads them back through the size-1 operand pointers).  Every block of
+    // the launch has finished its own work by now -- this block drew the last ticket -- so a
+    // size-1 array the group's blocks read in their prologue may be overwritten here.
+    void scalar_tail() {
+        if (g.tail.empty()) return;
+        const GroupIR& S = g.tail[0];
+        Gen sg{S, {}, {}};
+        sg.pfx = "S";
+        size_t sc_base = g.scalars.size(), bc_base = g.bcast_names.size();
+        if (!g.producer.empty()) {
+            sc_base += g.producer[0].scalars.size();
+            bc_base += g.producer[0].bcast_names.size();
+        }
+        const size_t so_base = g.souts.size();
+        o << "    if (threadIdx.x == 0) {\n";
+        for (size_t i = 0; i < S.scalars.size(); ++i)
+            o << "      const T Sc" << i << " = (T)a.sc[" << (sc_base + i) << "];\n";
+        for (size_t i = 0; i < S.bcast_names.size(); ++i)
+            o << "      const T Sb" << i << " = *(const volatile T*)a.bc[" << (bc_base + i) << "];\n";
+        for (size_t i = 0; i < S.roots.size(); ++i) {
+            const RootIR& r = S.roots[i];
+            if (r.domain != DOM_SCALAR) continue;
+            o << "      const T Sr" << i << " = " << sg.expr(r.opcode, sg.val(r.a, 0), sg.val(r.b, 0)) << ";\n";
+        }
+        for (size_t i = 0; i < S.souts.size(); ++i)
+            o << "      *(T*)a.sout[" << (so_base + i) << "] = " << sg.val(S.souts[i].value, 0) << ";\n";
+        o << "    }\n";
     }
 
     std::string guard(int domain, int e) const {

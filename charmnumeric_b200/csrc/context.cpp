@@ -42,6 +42,7 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_FUSE_PRODUCERS")) fuse_producers_ = std::max(0, std::min(2, atoi(f)));
     if (const char* f = getenv("CN_STENCIL_SHFL")) stencil_shfl_ = atoi(f) != 0;
     if (const char* f = getenv("CN_DEPENDENT_LAUNCH")) dependent_launch_ = atoi(f) != 0;
+    if (const char* f = getenv("CN_FUSE_SCALAR_TAIL")) fuse_scalar_tail_ = atoi(f) != 0;
     if (const char* f = getenv("CN_STENCIL_BLOCKS")) shifted_minb_ = std::max(1, std::min(8, atoi(f)));
     if (const char* f = getenv("CN_FLAT_BLOCKS")) flat_minb_ = std::max(1, std::min(8, atoi(f)));
     if (const char* f = getenv("CN_PLAN_CACHE")) plan_cache_ = atoi(f) != 0;
@@ -732,9 +733,12 @@ int Context::run_plan(Plan& plan) {
     for (PlanStep& st : plan.steps) {
         int rc;
         if (st.group) {
-            stats_.nodes += 1 + (long long)st.fused;
+            stats_.nodes += 1 + (long long)(st.fused + st.tails);
             rc = run_lowered(st.g, st.k);
-            if (rc == CN_OK) stats_.fused_reductions += (long long)st.fused;
+            if (rc == CN_OK) {
+                stats_.fused_reductions += (long long)st.fused;
+                stats_.scalar_tails += (long long)st.tails;
+            }
         } else {
             size_t i = st.index;
             rc = execute_node(plan.dag, &i);
@@ -882,6 +886,36 @@ int Context::execute_node(const Dag& dag, size_t* index) {
                 if ((rc = lower_group(*gnode, fused, &probe, &err_))) return rc;
             }
         }
+        // A scalar-only node behind the fused reductions (beta = r.r / rtr; res = sum) is
+        // evaluated by the thread that finishes the reductions.  On several ranks that needs
+        // the reductions finished inside the kernel (peer mailboxes), not by a collective
+        // behind it.
+        size_t tail_nodes = 0;
+        if (fuse_scalar_tail_ && probe.cls == GroupIR::SHIFTED && !probe.reds.empty() && probe.tail.empty() &&
+            j < dag.nodes.size() && is_group_node(dag.nodes[j]) && (nranks_ == 1 || peer_.ready)) {
+            GroupIR t;
+            std::string terr;
+            if (lower_group(dag.nodes[j], {}, &t, &terr) == CN_OK && t.cls == GroupIR::SCALAR_ONLY &&
+                t.dtype == probe.dtype && !t.souts.empty()) {
+                size_t sc = probe.scalars.size() + t.scalars.size(), bc = probe.bcast_names.size() + t.bcast_names.size();
+                if (!probe.producer.empty()) {
+                    sc += probe.producer[0].scalars.size();
+                    bc += probe.producer[0].bcast_names.size();
+                }
+                bool fits = sc <= CN_MAX_SC && bc <= CN_MAX_BC && probe.souts.size() + t.souts.size() <= CN_MAX_SOUT;
+                // a size-1 result of the group itself goes to a fresh buffer that is swapped in
+                // after the launch: the tail could not read it, nor write the same array
+                for (auto& so : probe.souts) {
+                    for (int name : t.bcast_names) fits = fits && name != so.name;
+                    for (auto& ts : t.souts) fits = fits && ts.name != so.name;
+                }
+                if (fits) {
+                    probe.tail.push_back(t);
+                    tail_nodes = 1;
+                    ++j;
+                }
+            }
+        }
         CompiledGroup* k = nullptr;
         if ((rc = get_kernel(probe, &k))) return rc;
         if (recording_) {
@@ -889,6 +923,7 @@ int Context::execute_node(const Dag& dag, size_t* index) {
             st.index = *index;
             st.group = true;
             st.fused = fused.size();
+            st.tails = tail_nodes;
             st.g = probe;
             st.k = k;
             recording_->steps.push_back(std::move(st));
@@ -896,7 +931,8 @@ int Context::execute_node(const Dag& dag, size_t* index) {
         int rc2 = run_lowered(probe, k);
         if (rc2) return rc2;
         stats_.fused_reductions += (long long)fused.size();
-        stats_.nodes += (long long)fused.size();
+        stats_.nodes += (long long)(fused.size() + tail_nodes);
+        stats_.scalar_tails += (long long)tail_nodes;
         *index = j;
         return CN_OK;
     }

@@ -79,6 +79,7 @@ struct PlanStep {
     size_t index = 0;     // node this step starts at
     bool group = false;   // a lowered group (g, k valid); otherwise the node runs generically
     size_t fused = 0;     // REDUCE / SUM nodes folded into the group
+    size_t tails = 0;     // scalar-only nodes folded in behind them
     GroupIR g;
     CompiledGroup* k = nullptr;
 };
@@ -107,6 +108,7 @@ struct Stats {
     long long halo_pushes = 0;       // kernels that stored their edge rows into the neighbours' mailboxes themselves
     long long row_fetches = 0;       // operands whose rows were fetched from other ranks for a strided group
     long long inlined_producers = 0; // whole-array assignments folded into the stencil kernel that reads them
+    long long scalar_tails = 0;      // scalar-only nodes evaluated inside the kernel that finished the reductions they read
 };
 
 struct DriverApi {
@@ -182,6 +184,7 @@ public:
     void set_debug_drop_copies(bool on) { debug_drop_copies_ = on; plans_.clear(); }
     void set_flat_prefetch(int mode) { flat_prefetch_ = mode; plans_.clear(); }
     void set_fuse_producers(int mode) { fuse_producers_ = mode; plans_.clear(); }
+    void set_fuse_scalar_tail(bool on) { fuse_scalar_tail_ = on; plans_.clear(); }
     void set_stencil_shfl(bool on) { stencil_shfl_ = on; plans_.clear(); }
     void set_dependent_launch(bool on) { dependent_launch_ = on; }
     void set_plan_cache(bool on) { plan_cache_ = on; plans_.clear(); }
@@ -209,6 +212,7 @@ private:
     int execute_node(const Dag& dag, size_t* index);
     int run_plan(Plan& plan);
     int run_lowered(const GroupIR& g, CompiledGroup* k);
+    int bind_tail(const GroupIR& g, CnGroupArgs* a);
     int run_shifted(const GroupIR& g, CompiledGroup* k);
     int run_strided(const GroupIR& g, CompiledGroup* k);
     int run_scalar_only(const GroupIR& g, CompiledGroup* k);
@@ -251,6 +255,7 @@ private:
     int staged_ns_ = 0;               // ring depth of staged 3-D kernels (0: default)
     bool staged_tile_set_ = false;    // the staged tile shape was chosen by the caller
     bool tile_set_ = false;           // the tile shape of the other kernels was chosen by the caller
+    bool fuse_scalar_tail_ = true;    // a scalar-only node behind fused reductions runs inside their kernel
     int fuse_producers_ = 2;          // a whole-array assignment + the stencil that reads it as one kernel:
                                       // 0 never, 1 recomputed per stencil point, 2 staged in shared memory where it fits
     // generated kernels are launched with programmatic stream serialisation: a kernel's launch

@@ -355,6 +355,50 @@ int Context::bind_reductions(const GroupIR& g, CnGroupArgs* a, int grid, std::ve
     return CN_OK;
 }
 
+// Launch arguments of a group's scalar tail: literal scalars, size-1 operands and size-1
+// results behind the group's (and its producer's) own.  Runs after bind_reductions, so that a
+// reduction result the tail reads exists.  Results are written in place: the tail runs after
+// every block of the launch has finished.
+int Context::bind_tail(const GroupIR& g, CnGroupArgs* a) {
+    const GroupIR& t = g.tail[0];
+    size_t sc_base = g.scalars.size(), bc_base = g.bcast_names.size();
+    if (!g.producer.empty()) {
+        sc_base += g.producer[0].scalars.size();
+        bc_base += g.producer[0].bcast_names.size();
+    }
+    const size_t so_base = g.souts.size();
+    if (sc_base + t.scalars.size() > CN_MAX_SC || bc_base + t.bcast_names.size() > CN_MAX_BC ||
+        so_base + t.souts.size() > CN_MAX_SOUT)
+        return fail(CN_ERR_LIMIT, "scalar tail does not fit the launch arguments");
+    for (size_t i = 0; i < t.scalars.size(); ++i) a->sc[sc_base + i] = t.scalars[i];
+    // results first: creating one may move the table, and operand pointers are taken after
+    for (size_t i = 0; i < t.souts.size(); ++i) {
+        const ScalarOutIR& so = t.souts[i];
+        Array* s = find(so.name);
+        if (!s) {
+            if (so.is_set) return fail(CN_ERR_UNKNOWN_ARRAY, "SET_REGION target " + std::to_string(so.name) + " does not exist");
+            int64_t one[1] = {1};
+            int rc = create_array(so.name, 1, one, t.dtype, false, &s);
+            if (rc) return rc;
+        }
+        if (s->global_elems() != 1) return fail(CN_ERR_SHAPE_MISMATCH, "scalar result stored into a larger array");
+        if (s->dtype != t.dtype) return fail(CN_ERR_BAD_DTYPE, "scalar result dtype differs from the group dtype");
+    }
+    for (size_t i = 0; i < t.souts.size(); ++i) {
+        Array* s = find(t.souts[i].name);
+        a->sout[so_base + i] = s->buf.data;
+        s->mark_written();
+    }
+    for (size_t i = 0; i < t.bcast_names.size(); ++i) {
+        Array* s = find(t.bcast_names[i]);
+        if (!s) return fail(CN_ERR_UNKNOWN_ARRAY, "size-1 array " + std::to_string(t.bcast_names[i]) + " does not exist");
+        if (s->global_elems() != 1) return fail(CN_ERR_SHAPE_MISMATCH, "broadcast operand is not a size-1 array");
+        if (s->dtype != t.dtype) return fail(CN_ERR_BAD_DTYPE, "size-1 operand dtype differs from the group dtype");
+        a->bc[bc_base + i] = s->buf.data;
+    }
+    return CN_OK;
+}
+
 int Context::finish_reductions(const std::vector<Array*>& results, bool in_kernel) {
     if (nranks_ == 1) return CN_OK;
     if (in_kernel && peer_.ready) {  // already summed over the ranks inside the kernel
@@ -652,6 +696,9 @@ int Context::run_shifted(const GroupIR& g, CompiledGroup* k) {
         }
         for (size_t m = 0; m < outs.size(); ++m) outs[m] = find(g.outs[m].name);
     }
+
+    // (elements of the array table keep their addresses when the table grows)
+    if (!g.tail.empty() && (rc = bind_tail(g, &a))) return rc;
 
     std::vector<Array*> pushed;
     if (k->tile.push && ntiles > 0 && !overlap) plan_push(g, outs, ext, &a, &pushed);

@@ -92,6 +92,14 @@ struct GroupIR {
     std::vector<GroupIR> producer;
     int producer_target = -1;
 
+    // Scalar tail: a SCALAR_ONLY group (size-1 arrays in, size-1 arrays out) that directly
+    // follows a group with fused reductions and is evaluated by the thread that has just
+    // written the reduction results, instead of by a kernel of its own (CG's
+    // beta = r.r / rtr, rtr = r.r; a Jacobi sweep's res = sum).  Its literal scalars,
+    // size-1 operands and results take the slots behind the group's (and its producer's)
+    // own.  Empty, or exactly one element.
+    std::vector<GroupIR> tail;
+
     std::vector<LeafIR> leaves;
     std::vector<double> scalars;
     std::vector<int> bcast_names;

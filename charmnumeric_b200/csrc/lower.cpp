@@ -973,6 +973,7 @@ std::string GroupIR::key() const {
         s << ';';
     }
     if (!producer.empty()) s << "|P{" << producer[0].key() << "}";
+    if (!tail.empty()) s << "|T{" << tail[0].key() << "}";
     return s.str();
 }
 

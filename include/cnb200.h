@@ -146,6 +146,13 @@ int cn_group_compile_check(const char* node_blob, int64_t size, char* source, in
 int cn_fuse_check(const char* node_a, int64_t size_a, const char* node_b, int64_t size_b,
                   char* source, int64_t cap, int* fused, char* err, int errcap);
 
+/* Host-only: a DAG of one group node, one or more REDUCE / SUM nodes the group's kernel can take
+ * in, and a last node of size-1 arithmetic (CG's beta = r.r / rtr; rtr = r.r).  *fused = 1 and the
+ * CUDA source of the single kernel when the last node runs as that kernel's scalar tail (see
+ * option "fuse_scalar_tail") and the kernel compiles for sm_100a; *fused = 0 otherwise. */
+int cn_tail_check(const char* dag_blob, int64_t size, char* source, int64_t cap, int* fused,
+                  char* err, int errcap);
+
 /* Host-only region algebra of the slab planner, on (start, stop, step) triples of row indices.
  * cn_region_intersect: common rows of two stepped regions (ArrayRegion intersect,
  * src/array_region.hpp:136-222).  cn_region_map: `part` is a piece of view `from`; the result is
@@ -238,6 +245,7 @@ typedef struct cn_stats {
     int64_t inlined_producers; /* whole-array assignments folded into the stencil kernel behind them */
     int64_t row_fetches;       /* operands of strided groups whose rows were fetched from other ranks */
     int64_t halo_pushes;       /* outputs whose edge rows the producing kernel stored into the neighbours' mailboxes */
+    int64_t scalar_tails;      /* scalar-only nodes evaluated inside the kernel that finished the reductions they read */
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
@@ -270,6 +278,10 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
  * registers cost the sweep more than the exchange launch they save -- so it is off),
  * "stencil_shfl" 0/1 (default 0, measured slower: cache-served stencil kernels take the
  * neighbours along the last dimension from neighbour lanes by warp shuffle),
+ * "fuse_scalar_tail" 0/1 (default 1: a scalar-only node that directly follows a group with fused
+ * reductions -- CG's beta = r.r / rtr, rtr = r.r; a Jacobi sweep's res = sum -- is evaluated by
+ * the thread that has just finished those reductions instead of by a kernel of its own; on
+ * several ranks only with "p2p"),
  * "dependent_launch" 0/1 (default 1: generated kernels are launched with programmatic stream
  * serialisation: a kernel's launch is released when the blocks of the kernel before it have
  * exited instead of after that kernel has drained, and every kernel waits for its

@@ -98,3 +98,27 @@ def test_register_cap_keeps_results(blocks, capfd):
     assert wide and min(wide) > 40, regs
     if blocks != "1":
         assert sweep and max(sweep) <= 40, regs
+
+
+def test_scalar_tail_on_and_off_agree(interface):
+    """`res[...] = sum(d * d)` behind a sweep with a fused reduction: with the tail folded into
+    the sweep's kernel and as a kernel of its own, the bits are the same and match the oracle."""
+    ctx = interface.context
+    try:
+        ctx.set_option("fuse_scalar_tail", 0)
+        before = ctx.stats()
+        off = _check(interface, _sweeps)
+        mid = ctx.stats()
+        ctx.set_option("fuse_scalar_tail", 1)
+        on = _check(interface, _sweeps)
+        after = ctx.stats()
+    finally:
+        ctx.set_option("fuse_scalar_tail", 1)
+    assert mid["scalar_tails"] == before["scalar_tails"]
+    # inside one DAG the frontend puts size-1 arithmetic into the group that follows it; only
+    # the last residual's `res[...] = s` stands alone behind its reduction
+    tails = after["scalar_tails"] - mid["scalar_tails"]
+    assert tails >= 1
+    assert (after["kernel_launches"] - mid["kernel_launches"]) == (mid["kernel_launches"] - before["kernel_launches"]) - tails
+    for k in off:
+        assert off[k].tobytes() == on[k].tobytes(), k

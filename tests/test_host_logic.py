@@ -318,3 +318,40 @@ def test_direction_update_and_stencil_compile_as_one_kernel():
     nodes = _pending_nodes()
     assert fuse_check(nodes[0], nodes[-1]) is None
     cnp.reset_frontend_state()
+
+
+def test_scalar_node_behind_a_fused_reduction_compiles_into_its_kernel():
+    """Host side of the scalar tail: CG's x, r update with its fused r.r, followed by
+    beta = r.r / rtr and rtr = r.r on size-1 arrays, is one kernel whose finishing thread
+    evaluates the size-1 arithmetic."""
+    from charmnumeric_b200.context import tail_check
+    from charmnumeric_b200 import wire
+    cnp.reset_frontend_state()
+    m = 66
+    x, r, p, Ap = (cnp.zeros((m, m)) for _ in range(4))
+    alpha, beta, rtr = cnp.zeros((1,)), cnp.zeros((1,)), cnp.zeros((1,))
+    F._state.pending = []
+    x[...] = x + alpha * p
+    r[...] = r - alpha * Ap
+    rr = cnp.dot2d(r, r)
+    beta[...] = rr / rtr
+    rtr[...] = rr
+    nodes = _pending_nodes()
+    assert len(nodes) == 3, [len(n.roots) for n in nodes]
+    src = tail_check(wire.dag_blob(nodes))
+    assert src is not None
+    tail = src[src.index("cn_sum_partials"):]
+    # operands of the tail sit behind the group's own size-1 operand (alpha): r.r and rtr
+    assert "Sb0" in tail and "Sb1" in tail and "a.sout[0]" in tail and "a.sout[1]" in tail
+    assert tail.index("a.red[0]") < tail.index("Sb0")     # results are stored before they are read back
+    # a last node that is not size-1 arithmetic is no tail
+    cnp.reset_frontend_state()
+    F._state.pending = []
+    x2, r2 = cnp.zeros((m, m)), cnp.zeros((m, m))
+    F._state.pending = []
+    r2[...] = r2 - 0.5 * x2
+    rr2 = cnp.dot2d(r2, r2)
+    x2[...] = x2 + rr2 * r2
+    nodes = _pending_nodes()
+    assert len(nodes) == 3 and tail_check(wire.dag_blob(nodes)) is None
+    cnp.reset_frontend_state()
