@@ -255,7 +255,11 @@ private:
     int staged_ns_ = 0;               // ring depth of staged 3-D kernels (0: default)
     bool staged_tile_set_ = false;    // the staged tile shape was chosen by the caller
     bool tile_set_ = false;           // the tile shape of the other kernels was chosen by the caller
-    bool fuse_scalar_tail_ = true;    // a scalar-only node behind fused reductions runs inside their kernel
+    // a scalar-only node behind fused reductions runs inside their kernel.  One launch fewer per
+    // CG iteration and per residual sweep, but no time: with dependent launches the size-1 kernel
+    // costs nothing measurable (CG 8192^2 890.6 against 891.4 us, Jacobi2D 10.27 against
+    // 10.21 us per step), so the option is off
+    bool fuse_scalar_tail_ = false;
     int fuse_producers_ = 2;          // a whole-array assignment + the stencil that reads it as one kernel:
                                       // 0 never, 1 recomputed per stencil point, 2 staged in shared memory where it fits
     // generated kernels are launched with programmatic stream serialisation: a kernel's launch

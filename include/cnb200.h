@@ -278,7 +278,7 @@ int cn_get_stats(cn_context* ctx, cn_stats* out);
  * registers cost the sweep more than the exchange launch they save -- so it is off),
  * "stencil_shfl" 0/1 (default 0, measured slower: cache-served stencil kernels take the
  * neighbours along the last dimension from neighbour lanes by warp shuffle),
- * "fuse_scalar_tail" 0/1 (default 1: a scalar-only node that directly follows a group with fused
+ * "fuse_scalar_tail" 0/1 (default 0, measured without effect on time: a scalar-only node that directly follows a group with fused
  * reductions -- CG's beta = r.r / rtr, rtr = r.r; a Jacobi sweep's res = sum -- is evaluated by
  * the thread that has just finished those reductions instead of by a kernel of its own; on
  * several ranks only with "p2p"),

@@ -113,7 +113,7 @@ def test_scalar_tail_on_and_off_agree(interface):
         on = _check(interface, _sweeps)
         after = ctx.stats()
     finally:
-        ctx.set_option("fuse_scalar_tail", 1)
+        ctx.set_option("fuse_scalar_tail", 0)
     assert mid["scalar_tails"] == before["scalar_tails"]
     # inside one DAG the frontend puts size-1 arithmetic into the group that follows it; only
     # the last residual's `res[...] = s` stands alone behind its reduction
