@@ -303,6 +303,39 @@ def cpu_baseline(workload, scale, steps, threads):
     raise ValueError(workload)
 
 
+def cpu_baseline_tiled(workload, scale, steps, pes):
+    """The reference-structured variant of the CPU baseline (CG and Jacobi2D): every array a
+    grid of separately allocated tiles (tile size by the reference's rule for `pes` PEs and an
+    overdecomposition factor of 4), one worker thread per PE, halo rows and columns packed
+    into messages and copied on receive, every node into a result buffer and copied back, dot
+    products as passes of their own.  Returns a dict for the JSON line, or None."""
+    import numpy as np
+    from oracle import oracle as O
+    lib = O.clib()
+    secs = np.zeros(1)
+    if workload == "cg":
+        n = max(8, int(8192 * scale))
+        m = n + 2
+        b = np.zeros((m, m))
+        b[1:-1, 1:-1] = O.randu((m, m), 0x5EED + 3)[1:-1, 1:-1]
+        hist = np.zeros(steps)
+        lib.cno_cg_poisson_tiled(O._ptr(b), None, m, steps, O._ptr(hist), 0, int(pes), O._ptr(secs))
+        extent = m
+    elif workload == "jacobi2d":
+        n = max(8, int(2048 * scale))
+        u = O.randu((n, n), 0x5EED + 1)
+        res = np.zeros(steps // 10 + 1)
+        lib.cno_jacobi2d_tiled(O._ptr(u), n, 0.25, steps, 10, O._ptr(res), 0, int(pes), O._ptr(secs))
+        extent = n
+    else:
+        return None
+    tile = int(lib.cno_tile(extent, 2, 4 * int(pes)))
+    per_dim = (extent + tile - 1) // tile
+    return {"value": steps / float(secs[0]), "cores": int(pes), "tile": tile, "tiles": per_dim * per_dim,
+            "what": ("tiles as separate allocations, one worker per PE, packed halo messages, "
+                     "result buffer + copy per node, separate dot passes")}
+
+
 def run_reference(args, rank, world):
     """The CPU arm: the oracle's loops for the named workload on all host cores, rank 0 only.
     It runs the per-GPU problem of the N = 1 run once; its configuration block and its step
@@ -330,6 +363,9 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    tiled = cpu_baseline_tiled(args.workload, args.scale, max(1, K // 2), threads)
+    if tiled:
+        line["cpu_baseline"]["tiled"] = tiled
     print(json.dumps(line), flush=True)
 
 
@@ -519,6 +555,13 @@ def measure(name, args, itf, dist, rank, world, local_rank, primary):
                     # the reference's own test set-up runs on four PEs (charmrun +p4)
                     v4, _ = cpu_baseline(name, args.scale, max(1, budget_steps[name] // 2), 4)
                     entry["cpu_baseline"]["p4"] = {"value": v4, "cores": 4}
+                # the same arithmetic laid out as the reference runs it (tiles, messages, copies)
+                tiled = cpu_baseline_tiled(name, args.scale, max(1, budget_steps[name] // 2), threads)
+                if tiled:
+                    entry["cpu_baseline"]["tiled"] = tiled
+                    if threads > 4 and primary:
+                        entry["cpu_baseline"]["tiled_p4"] = cpu_baseline_tiled(
+                            name, args.scale, max(1, budget_steps[name] // 3), 4)
             except Exception as exc:  # the baseline is a report, never a gate
                 entry["cpu_baseline"] = {"error": repr(exc)}
     wl.release()

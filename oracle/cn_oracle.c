@@ -419,3 +419,299 @@ void cno_power_iteration(const double* A, double* x, double* y, int64_t n, int s
         if (norm_hist) norm_hist[it] = s;
     }
 }
+
+/* ---- reference-structured variants (timing baseline) ---------------------------------------
+ * The same arithmetic as cno_jacobi2d / cno_cg_poisson, laid out the way the reference's CPU
+ * path runs it: every array is a grid of tiles, each tile its own allocation (one chare per
+ * tile, src/backend.hpp:93-200); a worker thread per "PE" owns the tiles t with
+ * t % npe == its number and visits them one DAG node at a time; a stencil node first packs
+ * the edge rows and columns of every tile into a message and copies the message into the
+ * neighbour's receive buffer (pack + copy on receive, src/executor_core.cpp:92-114,
+ * src/partition_comm.cpp:25-61), then evaluates every tile into a result buffer and copies
+ * the result into the target tile (src/execute_node.cpp:1581-1584); an axpy is a node of
+ * its own with its own result buffer and copy; a dot is its own pass, one partial per tile,
+ * partials added in tile order.  Elementwise results are bit-identical to the untiled
+ * functions; dots differ by summation order only (2-D tiles against flat ranges). */
+
+typedef struct {
+    int64_t m, T, nt;   /* m x m points, tiles of T x T (the last row / column of tiles smaller) */
+    double** t;         /* nt * nt tiles, row-major inside a tile with pitch = its own width */
+} cno_grid;
+
+static int64_t cno_th(const cno_grid* g, int64_t ti) { return ti * g->T + g->T <= g->m ? g->T : g->m - ti * g->T; }
+
+static void cno_grid_alloc(cno_grid* g, int64_t m, int64_t T) {
+    g->m = m;
+    g->T = T;
+    g->nt = (m + T - 1) / T;
+    g->t = (double**)malloc(sizeof(double*) * (size_t)(g->nt * g->nt));
+    for (int64_t ti = 0; ti < g->nt; ++ti)
+        for (int64_t tj = 0; tj < g->nt; ++tj)
+            g->t[ti * g->nt + tj] = (double*)calloc((size_t)(cno_th(g, ti) * cno_th(g, tj)), sizeof(double));
+}
+
+static void cno_grid_free(cno_grid* g) {
+    for (int64_t k = 0; k < g->nt * g->nt; ++k) free(g->t[k]);
+    free(g->t);
+}
+
+static void cno_grid_scatter(cno_grid* g, const double* a) {
+    for (int64_t ti = 0; ti < g->nt; ++ti)
+        for (int64_t tj = 0; tj < g->nt; ++tj) {
+            int64_t h = cno_th(g, ti), w = cno_th(g, tj);
+            for (int64_t i = 0; i < h; ++i)
+                memcpy(g->t[ti * g->nt + tj] + i * w, a + (ti * g->T + i) * g->m + tj * g->T, sizeof(double) * (size_t)w);
+        }
+}
+
+static void cno_grid_gather(const cno_grid* g, double* a) {
+    for (int64_t ti = 0; ti < g->nt; ++ti)
+        for (int64_t tj = 0; tj < g->nt; ++tj) {
+            int64_t h = cno_th(g, ti), w = cno_th(g, tj);
+            for (int64_t i = 0; i < h; ++i)
+                memcpy(a + (ti * g->T + i) * g->m + tj * g->T, g->t[ti * g->nt + tj] + i * w, sizeof(double) * (size_t)w);
+        }
+}
+
+/* Receive buffers of one tile: the neighbours' facing row / column (up, down, left, right). */
+typedef struct { double *up, *down, *left, *right; } cno_halo;
+
+static cno_halo* cno_halo_alloc(const cno_grid* g) {
+    cno_halo* h = (cno_halo*)malloc(sizeof(cno_halo) * (size_t)(g->nt * g->nt));
+    for (int64_t k = 0; k < g->nt * g->nt; ++k) {
+        h[k].up = (double*)calloc((size_t)g->T, sizeof(double));
+        h[k].down = (double*)calloc((size_t)g->T, sizeof(double));
+        h[k].left = (double*)calloc((size_t)g->T, sizeof(double));
+        h[k].right = (double*)calloc((size_t)g->T, sizeof(double));
+    }
+    return h;
+}
+
+static void cno_halo_free(const cno_grid* g, cno_halo* h) {
+    for (int64_t k = 0; k < g->nt * g->nt; ++k) {
+        free(h[k].up);
+        free(h[k].down);
+        free(h[k].left);
+        free(h[k].right);
+    }
+    free(h);
+}
+
+/* Every tile packs its four edges and delivers them: message buffer, then copy on receive. */
+static void cno_exchange(const cno_grid* g, cno_halo* hb, int npe) {
+    const int64_t nt = g->nt;
+#pragma omp parallel num_threads(npe)
+    {
+        double* msg = (double*)malloc(sizeof(double) * (size_t)g->T);
+#ifdef _OPENMP
+        const int pe = omp_get_thread_num(), np = omp_get_num_threads();
+#else
+        const int pe = 0, np = 1;
+#endif
+        for (int64_t k = pe; k < nt * nt; k += np) {
+            const int64_t ti = k / nt, tj = k % nt, h = cno_th(g, ti), w = cno_th(g, tj);
+            const double* a = g->t[k];
+            if (ti > 0) {           /* my first row is the upper neighbour's "down" */
+                memcpy(msg, a, sizeof(double) * (size_t)w);
+                memcpy(hb[(ti - 1) * nt + tj].down, msg, sizeof(double) * (size_t)w);
+            }
+            if (ti + 1 < nt) {
+                memcpy(msg, a + (h - 1) * w, sizeof(double) * (size_t)w);
+                memcpy(hb[(ti + 1) * nt + tj].up, msg, sizeof(double) * (size_t)w);
+            }
+            if (tj > 0) {           /* strided column: packed element by element */
+                for (int64_t i = 0; i < h; ++i) msg[i] = a[i * w];
+                memcpy(hb[ti * nt + tj - 1].right, msg, sizeof(double) * (size_t)h);
+            }
+            if (tj + 1 < nt) {
+                for (int64_t i = 0; i < h; ++i) msg[i] = a[i * w + w - 1];
+                memcpy(hb[ti * nt + tj + 1].left, msg, sizeof(double) * (size_t)h);
+            }
+        }
+        free(msg);
+    }
+}
+
+/* Value of the stencil input at local (i, j) of tile k, one step outside the tile allowed. */
+static inline double cno_at(const double* a, const cno_halo* hb, int64_t h, int64_t w, int64_t i, int64_t j) {
+    if (i < 0) return hb->up[j];
+    if (i >= h) return hb->down[j];
+    if (j < 0) return hb->left[i];
+    if (j >= w) return hb->right[i];
+    return a[i * w + j];
+}
+
+static double cno_now(void) {
+#ifdef _OPENMP
+    return omp_get_wtime();
+#else
+    return 0.0;
+#endif
+}
+
+static int cno_pe(void) {
+#ifdef _OPENMP
+    return omp_get_thread_num();
+#else
+    return 0;
+#endif
+}
+static int cno_np(void) {
+#ifdef _OPENMP
+    return omp_get_num_threads();
+#else
+    return 1;
+#endif
+}
+
+/* One pass over all tiles of up to three grids; `body` sees tile pointers and extents. */
+#define CNO_PRAGMA(x) _Pragma(#x)
+#define CNO_FOR_TILES(G, NPE, ...)                                                           \
+    CNO_PRAGMA(omp parallel num_threads(NPE)) {                                              \
+        double* res = (double*)malloc(sizeof(double) * (size_t)((G)->T * (G)->T));           \
+        const int pe_ = cno_pe(), np_ = cno_np();                                            \
+        for (int64_t k = pe_; k < (G)->nt * (G)->nt; k += np_) {                             \
+            const int64_t ti = k / (G)->nt, tj = k % (G)->nt;                                \
+            const int64_t h = cno_th((G), ti), w = cno_th((G), tj);                          \
+            (void)ti; (void)tj; (void)h; (void)w;                                            \
+            __VA_ARGS__                                                                      \
+        }                                                                                    \
+        free(res);                                                                           \
+    }
+
+static double cno_grid_dot(const cno_grid* a, const cno_grid* b, double* part, int npe) {
+    CNO_FOR_TILES(a, npe, {
+        const double* x = a->t[k];
+        const double* y = b->t[k];
+        double s = 0.0;
+        for (int64_t q = 0; q < h * w; ++q) s += x[q] * y[q];
+        part[k] = s;
+        (void)res;
+    })
+    double total = 0.0;
+    for (int64_t k = 0; k < a->nt * a->nt; ++k) total += part[k];
+    return total;
+}
+
+/* dst = a + s * b, as its own node: result buffer, then copy into the target tile */
+static void cno_grid_axpy(cno_grid* dst, const cno_grid* a, double s, const cno_grid* b, int sign, int npe) {
+    CNO_FOR_TILES(dst, npe, {
+        const double* x = a->t[k];
+        const double* y = b->t[k];
+        for (int64_t q = 0; q < h * w; ++q) {
+            double t = s * y[q];
+            res[q] = sign > 0 ? x[q] + t : x[q] - t;
+        }
+        memcpy(dst->t[k], res, sizeof(double) * (size_t)(h * w));
+    })
+}
+
+/* CG as cno_cg_poisson, tiles of T x T, npe worker threads.  x receives the solution (m x m,
+ * row-major); *seconds the time of the iterations alone (scatter / gather excluded). */
+void cno_cg_poisson_tiled(const double* b, double* x_out, int64_t m, int iters, double* rtr_hist,
+                          int64_t T, int npe, double* seconds) {
+    if (npe < 1) npe = 1;
+    if (T <= 0) T = cno_tile(m, 2, 4 * npe); /* overdecomposition factor 4, as `charmrun +pN` runs it */
+    cno_grid x, r, p, Ap;
+    cno_grid_alloc(&x, m, T);
+    cno_grid_alloc(&r, m, T);
+    cno_grid_alloc(&p, m, T);
+    cno_grid_alloc(&Ap, m, T);
+    cno_grid_scatter(&r, b);
+    cno_grid_scatter(&p, b);
+    cno_halo* hb = cno_halo_alloc(&p);
+    double* part = (double*)malloc(sizeof(double) * (size_t)(p.nt * p.nt));
+    const double t_start = cno_now();
+    double rtr = cno_grid_dot(&r, &r, part, npe);
+    for (int it = 0; it < iters; ++it) {
+        cno_exchange(&p, hb, npe);
+        const cno_grid* G = &p;
+        CNO_FOR_TILES(G, npe, {
+            const double* a = p.t[k];
+            const cno_halo* hk = &hb[k];
+            /* rows / columns of this tile that are interior points of the whole grid */
+            const int64_t i0 = ti == 0 ? 1 : 0, i1 = ti * T + h == m ? h - 1 : h;
+            const int64_t j0 = tj == 0 ? 1 : 0, j1 = tj * T + w == m ? w - 1 : w;
+            for (int64_t i = i0; i < i1; ++i)
+                for (int64_t j = j0; j < j1; ++j) {
+                    double t = 4.0 * a[i * w + j];
+                    t = t - cno_at(a, hk, h, w, i - 1, j);
+                    t = t - cno_at(a, hk, h, w, i + 1, j);
+                    t = t - cno_at(a, hk, h, w, i, j - 1);
+                    t = t - cno_at(a, hk, h, w, i, j + 1);
+                    res[i * w + j] = t;
+                }
+            for (int64_t i = i0; i < i1; ++i)
+                memcpy(Ap.t[k] + i * w + j0, res + i * w + j0, sizeof(double) * (size_t)(j1 - j0));
+        })
+        const double pAp = cno_grid_dot(&p, &Ap, part, npe);
+        const double alpha = rtr / pAp;
+        cno_grid_axpy(&x, &x, alpha, &p, +1, npe);
+        cno_grid_axpy(&r, &r, alpha, &Ap, -1, npe);
+        const double rtr_new = cno_grid_dot(&r, &r, part, npe);
+        const double beta = rtr_new / rtr;
+        cno_grid_axpy(&p, &r, beta, &p, +1, npe);
+        rtr = rtr_new;
+        if (rtr_hist) rtr_hist[it] = rtr_new;
+    }
+    if (seconds) *seconds = cno_now() - t_start;
+    if (x_out) cno_grid_gather(&x, x_out);
+    free(part);
+    cno_halo_free(&p, hb);
+    cno_grid_free(&x);
+    cno_grid_free(&r);
+    cno_grid_free(&p);
+    cno_grid_free(&Ap);
+}
+
+/* Jacobi2D as cno_jacobi2d on an n x n grid, tiles of T x T, npe worker threads; u is
+ * updated in place; res_out receives sum((new - old)^2) of every res_every-th sweep. */
+void cno_jacobi2d_tiled(double* u, int64_t n, double c, int iters, int res_every, double* res_out,
+                        int64_t T, int npe, double* seconds) {
+    if (npe < 1) npe = 1;
+    if (T <= 0) T = cno_tile(n, 2, 4 * npe);
+    cno_grid g;
+    cno_grid_alloc(&g, n, T);
+    cno_grid_scatter(&g, u);
+    cno_halo* hb = cno_halo_alloc(&g);
+    double* part = (double*)malloc(sizeof(double) * (size_t)(g.nt * g.nt));
+    int nres = 0;
+    const double t_start = cno_now();
+    for (int it = 1; it <= iters; ++it) {
+        const int want = res_every > 0 && (it % res_every) == 0;
+        cno_exchange(&g, hb, npe);
+        const cno_grid* G = &g;
+        CNO_FOR_TILES(G, npe, {
+            double* a = g.t[k];
+            const cno_halo* hk = &hb[k];
+            const int64_t i0 = ti == 0 ? 1 : 0, i1 = ti * T + h == n ? h - 1 : h;
+            const int64_t j0 = tj == 0 ? 1 : 0, j1 = tj * T + w == n ? w - 1 : w;
+            double s = 0.0;
+            for (int64_t i = i0; i < i1; ++i)
+                for (int64_t j = j0; j < j1; ++j) {
+                    double t = cno_at(a, hk, h, w, i - 1, j) + cno_at(a, hk, h, w, i + 1, j);
+                    t = t + cno_at(a, hk, h, w, i, j - 1);
+                    t = t + cno_at(a, hk, h, w, i, j + 1);
+                    const double v = c * t;
+                    res[i * w + j] = v;
+                    if (want) {
+                        const double d = v - a[i * w + j];
+                        s += d * d;
+                    }
+                }
+            part[k] = s;
+            for (int64_t i = i0; i < i1; ++i)
+                memcpy(a + i * w + j0, res + i * w + j0, sizeof(double) * (size_t)(j1 - j0));
+        })
+        if (want) {
+            double total = 0.0;
+            for (int64_t k = 0; k < g.nt * g.nt; ++k) total += part[k];
+            res_out[nres++] = total;
+        }
+    }
+    if (seconds) *seconds = cno_now() - t_start;
+    cno_grid_gather(&g, u);
+    free(part);
+    cno_halo_free(&g, hb);
+    cno_grid_free(&g);
+}

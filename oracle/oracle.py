@@ -76,6 +76,8 @@ def clib():
         lib.cno_chain_sum.argtypes = [p, p, i64, i64]
         lib.cno_cg_poisson.argtypes = [p, p, p, p, p, i64, C.c_int, p, i64]
         lib.cno_power_iteration.argtypes = [p, p, p, i64, C.c_int, p, i64]
+        lib.cno_cg_poisson_tiled.argtypes = [p, p, i64, C.c_int, p, i64, C.c_int, p]
+        lib.cno_jacobi2d_tiled.argtypes = [p, i64, d, C.c_int, C.c_int, p, i64, C.c_int, p]
         _clib = lib
     return _clib
 

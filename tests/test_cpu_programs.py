@@ -190,3 +190,47 @@ def _load_golden():
 
 
 _load_golden()
+
+
+@pytest.mark.parametrize("n,tile,npe", [(40, 16, 3), (37, 8, 4), (33, 64, 2), (50, 7, 5)])
+def test_tiled_jacobi2d_matches_the_flat_loops(oracle_mod, n, tile, npe):
+    """The reference-structured timing variant (tiles as separate allocations, packed halo
+    messages, result buffer + copy, one worker per PE) computes the very bits of the flat
+    loops; the residuals differ by summation order only."""
+    iters = 12
+    u = oracle_mod.randu((n, n), 0x5EED + 1)
+    u[0, :] = 1.0
+    u[-1, :] = 0.0
+    u[:, 0] = 0.0
+    u[:, -1] = 0.0
+    v = u.copy()
+    scratch = np.zeros_like(u)
+    res_flat, res_tiled = np.zeros(3), np.zeros(3)
+    lib = oracle_mod.clib()
+    lib.cno_jacobi2d(oracle_mod._ptr(u), oracle_mod._ptr(scratch), n, n, 0.25, iters, 5,
+                     oracle_mod._ptr(res_flat), 16)
+    secs = np.zeros(1)
+    lib.cno_jacobi2d_tiled(oracle_mod._ptr(v), n, 0.25, iters, 5, oracle_mod._ptr(res_tiled), tile, npe,
+                           oracle_mod._ptr(secs))
+    assert v.tobytes() == u.tobytes()
+    np.testing.assert_allclose(res_tiled[:2], res_flat[:2], rtol=1e-12)
+    assert secs[0] >= 0.0
+
+
+@pytest.mark.parametrize("m,tile,npe", [(18, 8, 3), (35, 16, 4), (34, 64, 1), (41, 5, 6)])
+def test_tiled_cg_matches_the_flat_loops(oracle_mod, m, tile, npe):
+    iters = 8
+    b = np.zeros((m, m))
+    b[1:-1, 1:-1] = oracle_mod.randu((m, m), 0x5EED + 3)[1:-1, 1:-1]
+    x, r, p, Ap = (np.zeros((m, m)) for _ in range(4))
+    hist, hist_t = np.zeros(iters), np.zeros(iters)
+    lib = oracle_mod.clib()
+    lib.cno_cg_poisson(oracle_mod._ptr(b), oracle_mod._ptr(x), oracle_mod._ptr(r), oracle_mod._ptr(p),
+                       oracle_mod._ptr(Ap), m, iters, oracle_mod._ptr(hist), 64)
+    xt = np.zeros((m, m))
+    secs = np.zeros(1)
+    lib.cno_cg_poisson_tiled(oracle_mod._ptr(b), oracle_mod._ptr(xt), m, iters, oracle_mod._ptr(hist_t), tile,
+                             npe, oracle_mod._ptr(secs))
+    # same operations on every point; only the order of the dot products' partial sums differs
+    np.testing.assert_allclose(hist_t, hist, rtol=1e-10)
+    np.testing.assert_allclose(xt, x, rtol=1e-10, atol=1e-14)
