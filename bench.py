@@ -148,6 +148,10 @@ def dist_setup(world):
         return None
     import torch.distributed as dist
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    # The library's NCCL communicator carries set-up traffic, operand rows of stepped views and
+    # one-value collectives; halos and reduction totals go through the peer mailboxes.  NVLink
+    # multicast buffers are not worth their set-up for that (an explicit setting is respected).
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group(backend="gloo", rank=int(os.environ["RANK"]), world_size=world)
     return dist
 
