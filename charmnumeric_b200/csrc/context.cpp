@@ -81,6 +81,7 @@ Context::~Context() {
         if (kv.second.module && drv_.ModuleUnload) drv_.ModuleUnload(kv.second.module);
     if (partials_) cudaFree(partials_);
     if (counter_) cudaFree(counter_);
+    if (pinned_) cudaFreeHost(pinned_);
     if (scratch_) cudaFree(scratch_);
     if (peer_.ready) {
         for (int p = 0; p < nranks_; ++p)
@@ -175,6 +176,10 @@ int Context::init() {
     CN_DRV(FuncGetAttribute, "cuFuncGetAttribute")
     CN_DRV(TensorMapEncodeTiled, "cuTensorMapEncodeTiled")
     error_word_ = counter_ + 16;  // second cache line of the zeroed 256-byte scratch block
+    if (cudaHostAlloc((void**)&pinned_, kPinnedBytes, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        pinned_ = nullptr;  // small results then take the pageable path
+    }
 #undef CN_DRV
     initialised_ = true;
     return CN_OK;

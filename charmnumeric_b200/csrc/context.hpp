@@ -212,6 +212,7 @@ private:
     int execute_node(const Dag& dag, size_t* index);
     int run_plan(Plan& plan);
     int run_lowered(const GroupIR& g, CompiledGroup* k);
+    int report_error_word(unsigned int word);
     int bind_tail(const GroupIR& g, CnGroupArgs* a);
     int run_shifted(const GroupIR& g, CompiledGroup* k);
     int run_strided(const GroupIR& g, CompiledGroup* k);
@@ -322,6 +323,11 @@ private:
     TileConfig tile_;
     TileConfig staged_tile_;   // tile shape of the TMA-staged stencil kernels
     unsigned int* error_word_ = nullptr;  // set by a kernel whose bounded wait ran out
+    // 4 KiB of pinned host memory: small results (cn_get of a size-1 array) and the error word
+    // come back through it as truly asynchronous copies behind one synchronisation, instead
+    // of one staged copy into pageable memory each
+    unsigned char* pinned_ = nullptr;
+    enum { kPinnedBytes = 4096, kPinnedWord = 4096 - 64 };
 
     std::unordered_map<int, Array> arrays_;
     std::unordered_map<std::string, CompiledGroup> kernels_;

@@ -1502,9 +1502,14 @@ int Context::check_device_error() {
     if (waiting_launches_ == checked_launches_) return CN_OK;
     checked_launches_ = waiting_launches_;
     unsigned int word = 0;
-    int rc = cuda_fail(cudaMemcpyAsync(&word, error_word_, sizeof(word), cudaMemcpyDeviceToHost, stream_), "error word");
+    unsigned int* dst = pinned_ ? (unsigned int*)(pinned_ + kPinnedWord) : &word;
+    int rc = cuda_fail(cudaMemcpyAsync(dst, error_word_, sizeof(word), cudaMemcpyDeviceToHost, stream_), "error word");
     if (rc) return rc;
     if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize"))) return rc;
+    return report_error_word(*dst);
+}
+
+int Context::report_error_word(unsigned int word) {
     if (word) {
         cudaMemsetAsync(error_word_, 0, sizeof(word), stream_);
         return fail(CN_ERR_CUDA, word == 1 ? "a stencil kernel gave up waiting for a tile copy (results are incomplete)"
@@ -1523,6 +1528,21 @@ int Context::get(int name, int64_t count, int dtype, void* out) {
     if (!out) return fail(CN_ERR_INVALID_ARGUMENT, "get: null output buffer");
     const size_t esz = dtype_size(dtype);
     int rc;
+    if ((nranks_ == 1 || x->replicated) && pinned_ && count * esz <= (size_t)kPinnedWord) {
+        // a small result (the scalar a solver reads every step): result and error word travel
+        // as two asynchronous copies into pinned memory behind one synchronisation
+        if ((rc = cuda_fail(cudaMemcpyAsync(pinned_, x->buf.data, count * esz, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
+        const bool check = waiting_launches_ != checked_launches_;
+        if (check) {
+            checked_launches_ = waiting_launches_;
+            if ((rc = cuda_fail(cudaMemcpyAsync(pinned_ + kPinnedWord, error_word_, sizeof(unsigned int),
+                                                cudaMemcpyDeviceToHost, stream_), "error word"))) return rc;
+        }
+        if ((rc = cuda_fail(cudaStreamSynchronize(stream_), "cudaStreamSynchronize"))) return rc;
+        memcpy(out, pinned_, count * esz);
+        stats_.bytes_d2h += count * esz;
+        return check ? report_error_word(*(unsigned int*)(pinned_ + kPinnedWord)) : CN_OK;
+    }
     if (nranks_ == 1 || x->replicated) {
         if ((rc = cuda_fail(cudaMemcpyAsync(out, x->buf.data, count * esz, cudaMemcpyDeviceToHost, stream_), "get copy"))) return rc;
         stats_.bytes_d2h += count * esz;
