@@ -49,7 +49,7 @@ if str(ROOT) not in sys.path:
 
 PEAKS_FALLBACK_GBS = 6650.0
 ALL_WORKLOADS = ["cg", "jacobi2d", "jacobi3d", "chain", "matvec"]
-DEFAULT_HALO = {"jacobi2d": 32}  # rows per side at N > 1; every other workload uses 1
+DEFAULT_HALO = {"jacobi2d": 64}  # rows per side at N > 1; every other workload uses 1
 
 
 def measured_peak():

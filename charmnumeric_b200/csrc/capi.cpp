@@ -404,7 +404,7 @@ int cn_set_option(cn_context* ctx, const char* key, int64_t value) {
     if (!ctx || !key) return cn::CN_ERR_INVALID_ARGUMENT;
     std::string k(key);
     if (k == "halo") {
-        if (value < 0 || value > 32) return cn::CN_ERR_INVALID_ARGUMENT;
+        if (value < 0 || value > 64) return cn::CN_ERR_INVALID_ARGUMENT;
         ctx->impl.set_halo((int)value);
     } else if (k == "staged") {
         cn::set_staged_level((int)value);

@@ -50,7 +50,7 @@ Context::Context(int device, int rank, int nranks)
     if (const char* f = getenv("CN_DEEP_HALO")) deep_halo_ = atoi(f) != 0;
     if (const char* f = getenv("CN_HALO")) {
         int v = atoi(f);
-        if (v >= 0 && v <= 32) halo_ = v;
+        if (v >= 0 && v <= 64) halo_ = v;
     }
     staged_tile_.tx = 64;
     staged_tile_.r = 4;

@@ -249,7 +249,7 @@ typedef struct cn_stats {
 } cn_stats;
 int cn_get_stats(cn_context* ctx, cn_stats* out);
 
-/* Options: "halo" depth (rows per side, 0..32, default 1; set before creating arrays; with a depth
+/* Options: "halo" depth (rows per side, 0..64, default 1; set before creating arrays; with a depth
  * above the stencil's reach, sweeps without a fused reduction also update the halo rows they can
  * (the neighbour computes the same values), so one exchange serves several sweeps; "deep_halo" 0
  * switches that off),

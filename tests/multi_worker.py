@@ -37,6 +37,7 @@ def main():
         "jacobi2d": G._jacobi2d_program(67, 130, 6, res_every=3),
         "jacobi2d_small": G._jacobi2d_program(9, 8, 3),
         "jacobi2d_long": G._jacobi2d_program(67, 130, 23, res_every=5),
+        "jacobi2d_deep": G._jacobi2d_program(300, 130, 70, res_every=10),
         "jacobi3d_long": G._jacobi3d_program((26, 12, 34), 9),
         "jacobi3d": G._jacobi3d_program((19, 12, 34), 3),
         "cg": G._cg_poisson_program(34, 8),
