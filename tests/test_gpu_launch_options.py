@@ -122,3 +122,24 @@ def test_scalar_tail_on_and_off_agree(interface):
     assert (after["kernel_launches"] - mid["kernel_launches"]) == (mid["kernel_launches"] - before["kernel_launches"]) - tails
     for k in off:
         assert off[k].tobytes() == on[k].tobytes(), k
+
+
+def test_option_ranges(interface):
+    """cn_set_option checks its values: halo depth 0..64, switches by name, nothing unknown."""
+    from charmnumeric_b200._lib import CnError
+    ctx = interface.context
+    try:
+        ctx.set_option("halo", 64)
+        with pytest.raises(CnError):
+            ctx.set_option("halo", 65)
+        with pytest.raises(CnError):
+            ctx.set_option("halo", -1)
+        for key in ("dependent_launch", "fuse_scalar_tail"):
+            ctx.set_option(key, 1)
+            ctx.set_option(key, 0)
+        with pytest.raises(CnError):
+            ctx.set_option("no_such_option", 1)
+    finally:
+        ctx.set_option("halo", 1)
+        ctx.set_option("dependent_launch", 1)
+        ctx.set_option("fuse_scalar_tail", 0)
